@@ -1,0 +1,188 @@
+// Inverse of the quantizer, and expansion of the compacted code stream into
+// the tile-major kernel layout.
+//
+// Replaces dequantize_tensor (atlasinfer_core/quant/adaptive_quantizer.py:156-251).
+// The reference keeps a running offset into the code stream and, per block,
+// masks the whole outlier index list (:194-196, O(blocks x outliers)).  Here the
+// sorted outlier index list is binary-searched once per block boundary: the
+// number of outliers before a block both locates the block's outliers and
+// gives the block's offset into the compacted code stream (position minus
+// outliers before it), so every block is independent.
+#include "common.cuh"
+
+namespace atlas {
+namespace {
+
+constexpr int DQ_THREADS = 256;
+constexpr int DQ_SPAN = 4096;  // padded elements per CTA
+
+// first i in [0, n) with idx[i] >= key
+__device__ __forceinline__ int64_t lower_bound_i64(const int64_t *idx, int64_t n, int64_t key) {
+    int64_t lo = 0, hi = n;
+    while (lo < hi) {
+        int64_t mid = (lo + hi) >> 1;
+        if (idx[mid] < key) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+// Shared walk over one span of the padded tensor.  `emit(p, is_outlier, k, code)`
+// is called for every padded position p of the span: k is the outlier's index
+// in the outlier streams when is_outlier, else `code` is the int8 code.
+template <class Emit>
+__device__ __forceinline__ void walk_span(const int8_t *codes, int64_t n_codes, const int64_t *oidx,
+                                          int64_t n_out, int64_t padded, Emit emit) {
+    __shared__ int64_t s_lo, s_hi;
+    const int64_t span0 = (int64_t)blockIdx.x * DQ_SPAN;
+    const int64_t span1 = min(span0 + DQ_SPAN, padded);
+    if (threadIdx.x == 0) s_lo = lower_bound_i64(oidx, n_out, span0);
+    if (threadIdx.x == 32) s_hi = lower_bound_i64(oidx, n_out, span1);
+    __syncthreads();
+    const int64_t lo = s_lo, hi = s_hi;
+    for (int64_t p = span0 + threadIdx.x; p < span1; p += DQ_THREADS) {
+        // outliers of this span with index < p: search the (short) window [lo, hi)
+        int64_t a = lo, b = hi;
+        while (a < b) {
+            int64_t mid = (a + b) >> 1;
+            if (oidx[mid] < p) a = mid + 1; else b = mid;
+        }
+        const bool is_out = (a < hi) && (oidx[a] == p);
+        int8_t code = 0;
+        if (!is_out) {
+            const int64_t ci = p - a;  // position in the compacted stream
+            code = (ci < n_codes) ? codes[ci] : (int8_t)0;
+        }
+        emit(p, is_out, a, code);
+    }
+}
+
+__global__ void __launch_bounds__(DQ_THREADS)
+dequantize_kernel(const int8_t *codes, int64_t n_codes, const uint16_t *ovals, const int64_t *oidx,
+                  int64_t n_out, const uint16_t *scales, int64_t numel, int64_t padded, int bs,
+                  uint16_t *w) {
+    walk_span(codes, n_codes, oidx, n_out, padded, [&](int64_t p, bool is_out, int64_t k, int8_t code) {
+        if (p >= numel) return;
+        uint16_t v;
+        if (is_out) {
+            v = ovals[k];
+        } else {
+            // fp16(code) * scale, one fp16 rounding (adaptive_quantizer.py:216)
+            const float sc = __half2float(__ushort_as_half(scales[p / bs]));
+            v = __half_as_ushort(__float2half_rn(__fmul_rn((float)code, sc)));
+        }
+        w[p] = v;
+    });
+}
+
+// Byte offset of weight (row, col) inside the tile-major layout.
+__device__ __forceinline__ int64_t tile_offset(int64_t row, int64_t col, int64_t k_tiles) {
+    const int64_t rt = row >> 7, kt = col >> 6;
+    const int strip = (int)(row & 127) >> 4, h = (int)(row & 15) >> 3, g = (int)(row & 7);
+    const int tig = (int)(col & 63) >> 4, byte = (int)(col & 15);
+    return ((((rt * k_tiles + kt) * 8 + strip) * 2 + h) * 32 + (g * 4 + tig)) * 16 + byte;
+}
+
+__global__ void __launch_bounds__(DQ_THREADS)
+repack_kernel(const int8_t *codes, int64_t n_codes, const int64_t *oidx, int64_t n_out, int64_t n_rows,
+              int64_t n_cols, uint8_t *tiles, int32_t *ocol) {
+    const int64_t k_tiles = n_cols >> 6;
+    walk_span(codes, n_codes, oidx, n_out, n_rows * n_cols, [&](int64_t p, bool is_out, int64_t k, int8_t code) {
+        const int64_t row = p / n_cols, col = p - row * n_cols;
+        tiles[tile_offset(row, col, k_tiles)] = (uint8_t)((int)code + 128);
+        if (is_out) ocol[k] = (int32_t)col;
+    });
+}
+
+// Rows beyond n_rows inside the last 128-row tile: code 0.
+__global__ void __launch_bounds__(DQ_THREADS)
+repack_pad_kernel(int64_t n_rows, int64_t n_rows_padded, int64_t n_cols, uint8_t *tiles) {
+    const int64_t k_tiles = n_cols >> 6;
+    const int64_t total = (n_rows_padded - n_rows) * n_cols;
+    for (int64_t i = (int64_t)blockIdx.x * DQ_THREADS + threadIdx.x; i < total; i += (int64_t)gridDim.x * DQ_THREADS) {
+        const int64_t row = n_rows + i / n_cols, col = i % n_cols;
+        tiles[tile_offset(row, col, k_tiles)] = 128;
+    }
+}
+
+__global__ void __launch_bounds__(DQ_THREADS)
+row_ptr_kernel(const int64_t *oidx, int64_t n_out, int64_t n_rows, int64_t n_cols, int32_t *row_ptr) {
+    const int64_t r = (int64_t)blockIdx.x * DQ_THREADS + threadIdx.x;
+    if (r <= n_rows) row_ptr[r] = (int32_t)lower_bound_i64(oidx, n_out, r * n_cols);
+}
+
+}  // namespace
+}  // namespace atlas
+
+extern "C" {
+
+int atlas_dequantize(const int8_t *codes, int64_t n_codes, const void *outlier_vals,
+                     const int64_t *outlier_idx, int64_t n_outliers, const void *scales, int64_t numel,
+                     int block_size, void *w_out, void *stream) {
+    using namespace atlas;
+    clear_error();
+    ATLAS_RETURN_IF(numel < 0 || n_codes < 0 || n_outliers < 0 || block_size < 1, ATLAS_ERR_BAD_ARGUMENT,
+                    "atlas_dequantize: negative size or block_size < 1");
+    if (numel == 0) return ATLAS_OK;
+    const int64_t padded = ceil_div_i64(numel, block_size) * block_size;
+    ATLAS_RETURN_IF(n_codes + n_outliers != padded, ATLAS_ERR_BAD_ARGUMENT,
+                    "atlas_dequantize: %lld codes + %lld outliers do not cover %lld padded elements",
+                    (long long)n_codes, (long long)n_outliers, (long long)padded);
+    ATLAS_RETURN_IF(!w_out || !scales || (n_codes && !codes) || (n_outliers && (!outlier_vals || !outlier_idx)),
+                    ATLAS_ERR_BAD_ARGUMENT, "atlas_dequantize: null buffer");
+    int rc = check_device();
+    if (rc) return rc;
+    const int64_t grid = ceil_div_i64(padded, DQ_SPAN);
+    ATLAS_RETURN_IF(grid > 0x7fffffff, ATLAS_ERR_UNSUPPORTED, "atlas_dequantize: tensor too large");
+    dequantize_kernel<<<(unsigned)grid, DQ_THREADS, 0, (cudaStream_t)stream>>>(
+        codes, n_codes, (const uint16_t *)outlier_vals, outlier_idx, n_outliers, (const uint16_t *)scales,
+        numel, padded, block_size, (uint16_t *)w_out);
+    return check_cuda(cudaGetLastError(), "dequantize_kernel launch");
+}
+
+size_t atlas_tiles_bytes(int64_t n_rows, int64_t n_cols) {
+    if (n_rows <= 0 || n_cols <= 0) return 0;
+    return (size_t)(atlas::ceil_div_i64(n_rows, 128) * 128 * n_cols);
+}
+
+int atlas_repack(const int8_t *codes, int64_t n_codes, const int64_t *outlier_idx, int64_t n_outliers,
+                 int64_t n_rows, int64_t n_cols, int block_size, uint8_t *tiles, int32_t *outlier_row_ptr,
+                 int32_t *outlier_col, void *stream) {
+    using namespace atlas;
+    clear_error();
+    ATLAS_RETURN_IF(n_rows <= 0 || n_cols <= 0 || n_codes < 0 || n_outliers < 0 || block_size < 1,
+                    ATLAS_ERR_BAD_ARGUMENT, "atlas_repack: bad size");
+    ATLAS_RETURN_IF(n_cols % 64 != 0 || block_size % 16 != 0 || n_cols % block_size != 0,
+                    ATLAS_ERR_UNSUPPORTED,
+                    "atlas_repack: needs n_cols %% 64 == 0, block_size %% 16 == 0 and n_cols %% block_size == 0 "
+                    "(got n_cols=%lld block_size=%d)", (long long)n_cols, block_size);
+    ATLAS_RETURN_IF(n_cols > 0x7fffffff || n_outliers > 0x7fffffff, ATLAS_ERR_UNSUPPORTED,
+                    "atlas_repack: sizes beyond int32");
+    ATLAS_RETURN_IF(n_codes + n_outliers != n_rows * n_cols, ATLAS_ERR_BAD_ARGUMENT,
+                    "atlas_repack: %lld codes + %lld outliers do not cover %lld x %lld",
+                    (long long)n_codes, (long long)n_outliers, (long long)n_rows, (long long)n_cols);
+    ATLAS_RETURN_IF(!tiles || !outlier_row_ptr || (n_codes && !codes) || (n_outliers && (!outlier_idx || !outlier_col)),
+                    ATLAS_ERR_BAD_ARGUMENT, "atlas_repack: null buffer");
+    int rc = check_device();
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t numel = n_rows * n_cols;
+    const int64_t grid = ceil_div_i64(numel, DQ_SPAN);
+    ATLAS_RETURN_IF(grid > 0x7fffffff, ATLAS_ERR_UNSUPPORTED, "atlas_repack: tensor too large");
+    repack_kernel<<<(unsigned)grid, DQ_THREADS, 0, st>>>(codes, n_codes, outlier_idx, n_outliers, n_rows,
+                                                         n_cols, tiles, outlier_col);
+    rc = check_cuda(cudaGetLastError(), "repack_kernel launch");
+    if (rc) return rc;
+    const int64_t rows_padded = ceil_div_i64(n_rows, 128) * 128;
+    if (rows_padded > n_rows) {
+        const int64_t total = (rows_padded - n_rows) * n_cols;
+        const int64_t g = ceil_div_i64(total, DQ_THREADS);
+        repack_pad_kernel<<<(unsigned)(g < 4096 ? g : 4096), DQ_THREADS, 0, st>>>(n_rows, rows_padded, n_cols, tiles);
+        rc = check_cuda(cudaGetLastError(), "repack_pad_kernel launch");
+        if (rc) return rc;
+    }
+    row_ptr_kernel<<<(unsigned)ceil_div_i64(n_rows + 1, DQ_THREADS), DQ_THREADS, 0, st>>>(
+        outlier_idx, n_outliers, n_rows, n_cols, outlier_row_ptr);
+    return check_cuda(cudaGetLastError(), "row_ptr_kernel launch");
+}
+
+}  // extern "C"

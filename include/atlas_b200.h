@@ -1,0 +1,149 @@
+/*
+ * atlas_b200.h -- C ABI of the B200 (sm_100a) implementation of AtlasInfer's
+ * adaptive hybrid quantization path.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers and sizes,
+ * enqueues its work on the CUDA stream it is given and returns an int status
+ * (0 = ok).  The library owns no memory: every buffer, workspace included,
+ * belongs to the caller, and no pointer is kept after a call returns.  There
+ * is no CPU fallback; a call made without a usable GPU returns an error.
+ *
+ * fp16 / bf16 buffers are passed as `void*` (raw 16-bit patterns).
+ *
+ * Citations name files of the reference project (nishantkluhera/AtlasInfer).
+ */
+#ifndef ATLAS_B200_H_
+#define ATLAS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+/* Exported with default visibility; everything else in the library is hidden. */
+#if defined(__GNUC__)
+#define ATLAS_API __attribute__((visibility("default")))
+#else
+#define ATLAS_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define ATLAS_OK 0
+#define ATLAS_ERR_BAD_ARGUMENT 1   /* null pointer, negative size, bad dtype     */
+#define ATLAS_ERR_UNSUPPORTED 2    /* shape / block size outside the fast path   */
+#define ATLAS_ERR_CAPACITY 3       /* an output or workspace buffer is too small */
+#define ATLAS_ERR_LAUNCH 4         /* CUDA reported an error (see last_error)    */
+#define ATLAS_ERR_TIMEOUT 5        /* a bounded device-side wait ran out         */
+#define ATLAS_ERR_NO_DEVICE 6      /* no CUDA device / wrong architecture        */
+
+/* activation / output element types */
+#define ATLAS_DTYPE_F16 0
+#define ATLAS_DTYPE_BF16 1
+
+/* Library version (major*10000 + minor*100 + patch). */
+ATLAS_API int atlas_version(void);
+/* Text of the last error raised on the calling thread ("" if none). */
+ATLAS_API const char *atlas_last_error(void);
+/* Fixed text for a status code. */
+ATLAS_API const char *atlas_status_string(int status);
+
+/* ---- quantize ------------------------------------------------------------
+ * Replaces quantize_tensor(fp16_tensor, block_size, z_threshold)
+ * (atlasinfer_core/quant/adaptive_quantizer.py:51-148) for a tensor already in
+ * device memory.  The flat input is zero-padded to a whole number of blocks;
+ * per block the z-score outlier test (:44-49, :106-107), the fp16 scale
+ * absmax/127 (:121-123) and the int8 codes (:125-126) are evaluated exactly as
+ * PyTorch's CPU kernels do, so all four output streams are bit-identical to
+ * the reference's.
+ *
+ *   w              numel fp16 values
+ *   block_size     multiple of 32, 32..512 (others: ATLAS_ERR_UNSUPPORTED)
+ *   z_threshold    as given to the reference; rounded to fp16 inside
+ *   codes          capacity padded_numel int8  (compacted non-outlier codes)
+ *   outlier_vals   capacity outlier_capacity fp16
+ *   outlier_idx    capacity outlier_capacity int64 (flat index, padded tensor)
+ *   scales         n_blocks fp16
+ *   counts         4 x int64 on the device: [0] n_codes, [1] n_outliers
+ *                  (the true count even when it exceeds outlier_capacity, in
+ *                  which case only the first outlier_capacity entries were
+ *                  stored and the caller retries with more room), [2] non-zero
+ *                  if a bounded wait ran out (results invalid), [3] reserved
+ *   workspace      atlas_quantize_workspace_bytes(numel, block_size) bytes
+ *                  of scratch, 16-byte aligned; contents are irrelevant
+ *                  before and after the call
+ */
+ATLAS_API size_t atlas_quantize_workspace_bytes(int64_t numel, int block_size);
+ATLAS_API int atlas_quantize(const void *w, int64_t numel, int block_size, double z_threshold,
+                   int8_t *codes, void *outlier_vals, int64_t *outlier_idx,
+                   int64_t outlier_capacity, void *scales, int64_t *counts,
+                   void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- dequantize ------------------------------------------------------------
+ * Replaces dequantize_tensor(quant_data, target_device)
+ * (adaptive_quantizer.py:156-251) minus its id()-keyed cache: writes the
+ * numel fp16 values fp16(fp16(code) * scale) / raw outlier values (:216,
+ * :221-235).  Any block_size >= 1 and any numel are accepted.
+ */
+ATLAS_API int atlas_dequantize(const int8_t *codes, int64_t n_codes, const void *outlier_vals,
+                     const int64_t *outlier_idx, int64_t n_outliers, const void *scales,
+                     int64_t numel, int block_size, void *w_out, void *stream);
+
+/* ---- repack to the kernel layout -----------------------------------------------
+ * No counterpart in the reference (which re-derives positions per block at
+ * adaptive_quantizer.py:187-212 and caches an fp16 copy).  Expands the
+ * compacted code stream of a [n_rows, n_cols] weight into the dense,
+ * tile-major layout the linear kernels stream:
+ *
+ *   tiles          atlas_tiles_bytes(n_rows, n_cols) bytes; code + 128 as
+ *                  uint8 (outlier positions hold 128, i.e. code 0), ordered
+ *                  [row/128][col/64][(row%128)/16][(row%16)/8][(row%8)*4 +
+ *                  (col%64)/16][col%16]; rows padded to a multiple of 128
+ *   outlier_row_ptr  n_rows + 1 int32: CSR row starts into the outlier streams
+ *   outlier_col    n_outliers int32 column of each outlier
+ *
+ * Requires n_cols % 64 == 0 and n_cols % block_size == 0 with block_size a
+ * multiple of 16 (blocks never straddle rows), else ATLAS_ERR_UNSUPPORTED.
+ * Outliers in the padding cannot occur under that condition.
+ */
+ATLAS_API size_t atlas_tiles_bytes(int64_t n_rows, int64_t n_cols);
+ATLAS_API int atlas_repack(const int8_t *codes, int64_t n_codes, const int64_t *outlier_idx,
+                 int64_t n_outliers, int64_t n_rows, int64_t n_cols, int block_size,
+                 uint8_t *tiles, int32_t *outlier_row_ptr, int32_t *outlier_col, void *stream);
+
+/* ---- quantized linear forward ----------------------------------------------------
+ * Replaces QuantizedLinear.forward (integration/atlas_wrappers.py:30-74):
+ * y[m][n] = sum_k x[m][k] * W[n][k] + bias[n], W being the dequantized weight
+ * of dequantize_tensor, never materialised.  x and y share `dtype`
+ * (ATLAS_DTYPE_F16 as in the reference, or ATLAS_DTYPE_BF16); bias is fp16 or
+ * NULL.  ldx / ldy are row strides in elements.  bf16 activations are used
+ * as fp16 inside (|x| > 65504 saturates).
+ *
+ * atlas_qlinear_gemv: decode shapes, any m >= 1 (rows are processed in groups
+ * of up to 32; intended for m <= 32).  HBM-bound: streams tiles once per
+ * group, dequantises in registers and adds the outlier products in the same
+ * launch.
+ *
+ * atlas_qlinear_gemm: prefill shapes (m >= 128 intended, any m >= 1
+ * accepted).  Stages tiles through shared memory, dequantises to fp16
+ * operand tiles and multiplies with tcgen05 into TMEM accumulators.
+ * `workspace` must hold atlas_qlinear_gemm_workspace_bytes(m, n_cols) bytes.
+ */
+ATLAS_API int atlas_qlinear_gemv(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
+                       const void *scales, const int32_t *outlier_row_ptr,
+                       const int32_t *outlier_col, const void *outlier_vals, int64_t n_rows,
+                       int64_t n_cols, int block_size, const void *bias, void *y, int64_t ldy,
+                       void *stream);
+
+ATLAS_API size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_cols);
+ATLAS_API int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
+                       const void *scales, const int32_t *outlier_row_ptr,
+                       const int32_t *outlier_col, const void *outlier_vals, int64_t n_rows,
+                       int64_t n_cols, int block_size, const void *bias, void *y, int64_t ldy,
+                       void *workspace, size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATLAS_B200_H_ */

@@ -1,0 +1,69 @@
+"""Shared helpers of the test-suite: fixtures on disk and seeded synthetic weights."""
+import glob
+import os
+
+import numpy as np
+import torch
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def golden_names():
+    return sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+
+
+def _h(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).view(torch.float16)
+
+
+def load_golden(name):
+    """One fixture as torch tensors (fp16 fields re-viewed from their stored int16 patterns)."""
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    shape = tuple(int(v) for v in z["shape"])
+    rec = dict(
+        name=name, shape=shape, block_size=int(z["block_size"]), z_threshold=float(z["z_threshold"]),
+        input=_h(z["input"]).view(shape), fp8_data=torch.from_numpy(z["fp8_data"]),
+        fp16_outliers=_h(z["fp16_outliers"]), outlier_indices=torch.from_numpy(z["outlier_indices"]),
+        scale_factors=_h(z["scale_factors"]), dequantized=_h(z["dequantized"]).view(shape))
+    if "y" in z:
+        xs = tuple(int(v) for v in z["x_shape"])
+        rec.update(x=_h(z["x"]).view(xs), bias=_h(z["bias"]), y=_h(z["y"]).view(*xs[:-1], shape[0]))
+    return rec
+
+
+def bits(t):
+    """Raw bit patterns, so that fp16 tensors compare bit for bit (and -0.0 != 0.0)."""
+    return t.view(torch.int16) if t.dtype in (torch.float16, torch.bfloat16) else t
+
+
+def assert_streams_equal(got, want, what=""):
+    """All four quantizer streams bit-equal; ``got``/``want`` expose the QuantizedTensor field names."""
+    for f in ("fp8_data", "fp16_outliers", "outlier_indices", "scale_factors"):
+        a, b = getattr(got, f) if not isinstance(got, dict) else got[f], \
+               getattr(want, f) if not isinstance(want, dict) else want[f]
+        a, b = a.cpu(), b.cpu()
+        assert a.dtype == b.dtype, f"{what}{f}: dtype {a.dtype} != {b.dtype}"
+        assert a.shape == b.shape, f"{what}{f}: shape {tuple(a.shape)} != {tuple(b.shape)}"
+        if not torch.equal(bits(a), bits(b)):
+            bad = (bits(a) != bits(b)).nonzero().flatten()
+            raise AssertionError(f"{what}{f}: {bad.numel()} of {a.numel()} differ, first at {int(bad[0])}")
+
+
+def config_weights(rows, cols, seed, sigma=0.02):
+    """fp16 N(0, sigma) with 0.1 % of the entries (seeded positions) replaced by +-U(0.1, 0.5)."""
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(rows, cols, generator=g) * sigma
+    n = w.numel()
+    k = round(1e-3 * n)
+    pos = torch.randint(0, n, (k,), generator=g)
+    mag = torch.rand(k, generator=g) * 0.4 + 0.1
+    sign = torch.where(torch.rand(k, generator=g) < 0.5, -1.0, 1.0)
+    w.view(-1)[pos] = mag * sign
+    return w.to(torch.float16)
+
+
+def rel_max_err(y, ref):
+    """max|y - ref| / rms(ref): the linear outputs' tolerance metric (bound: 1e-2)."""
+    y, ref = y.double().cpu(), ref.double().cpu()
+    rms = ref.pow(2).mean().sqrt().item()
+    return (y - ref).abs().max().item() / max(rms, 1e-30)
