@@ -1,0 +1,443 @@
+#!/usr/bin/env python
+"""Benchmark of the adaptive hybrid quantization path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline metric (BASELINE.json): decode dequant-GEMV HBM GB/s on the
+Llama-2-7B-shaped quantized linears (32 layers x q/k/v/o 4096x4096, gate/up
+11008x4096, down 4096x11008), batch 1, bf16 activations.  One step = one pass
+over all 224 linears (6.5 G weights, 6.7 GB of quantized data: every step
+streams far more than the 126 MB L2, so nothing is served from cache).
+
+  value     algorithmic bytes of a step / device time, inputs resident in HBM,
+            the step replayed from a CUDA graph (one launch per linear)
+  e2e       the same pass through QuantizedLinear.forward with host activations:
+            per linear a pinned-host -> device copy of x and a device -> host
+            read of y inside the timed region
+  extra     the other two figures BASELINE.json names (prefill GEMM TFLOP/s,
+            quantize GB/s), GEMV at batch 4 and 16 and, with --gpus > 1, the
+            70B-shaped column-parallel decode (batch 32, NCCL all-gather)
+
+With --gpus N > 1 every rank runs the same pass on its own GPU (replicas, no
+collective: the path shards by independent tensors) and `value` is the sum over
+ranks / max time over ranks ("weak").  --impl reference times the CPU oracle
+port of the same linears on the host cores (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+LLAMA7B = dict(hidden=4096, inter=11008, layers=32)
+LLAMA7B_LINEARS = [("q_proj", 4096, 4096), ("k_proj", 4096, 4096), ("v_proj", 4096, 4096),
+                   ("o_proj", 4096, 4096), ("gate_proj", 11008, 4096), ("up_proj", 11008, 4096),
+                   ("down_proj", 4096, 11008)]
+LLAMA70B_LINEARS = [("q_proj", 8192, 8192), ("k_proj", 1024, 8192), ("v_proj", 1024, 8192),
+                    ("o_proj", 8192, 8192), ("gate_proj", 28672, 8192), ("up_proj", 28672, 8192),
+                    ("down_proj", 8192, 28672)]
+BLOCK = 128
+NO_GRAPH = False
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm=float(p["hbm_gbs"]), tf_burst=float(p["bf16_tflops"]),
+                    tf_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------- synthetic data
+def synth_weight(n, k, gen, sigma=0.02, device="cuda"):
+    """fp16 N(0, sigma) with 0.1 % of the entries replaced by +-U(0.1, 0.5) (seeded)."""
+    w = torch.randn(n, k, generator=gen, device=device) * sigma
+    cnt = round(1e-3 * n * k)
+    pos = torch.randint(0, n * k, (cnt,), generator=gen, device=device)
+    mag = torch.rand(cnt, generator=gen, device=device) * 0.4 + 0.1
+    sgn = torch.where(torch.rand(cnt, generator=gen, device=device) < 0.5, -1.0, 1.0)
+    w.view(-1)[pos] = mag * sgn
+    return w.to(torch.float16)
+
+
+def linear_bytes(n, k, n_out, m):
+    """Algorithmic bytes of one quantized linear call: codes + scales + outliers (2 B value,
+    4 B index) + activations in and out."""
+    return (n * k - n_out) + (n * k // BLOCK) * 2 + n_out * 6 + m * k * 2 + m * n * 2
+
+
+class Linear:
+    """Device-resident kernel image of one quantized linear (canonical code stream dropped)."""
+
+    def __init__(self, w, keep_module=False):
+        import atlasinfer_b200 as ab
+        from atlasinfer_b200.integration import atlas_wrappers as aw
+        q = ab.quantize_tensor(w)
+        self.n, self.k = w.shape
+        self.n_out = q.fp16_outliers.numel()
+        lay = aw.build_kernel_layout(q)
+        torch.cuda.current_stream().synchronize()
+        # the kernels read tiles / CSR / scales / outlier values; the compacted codes are not needed
+        slim = ab.QuantizedTensor(torch.empty(0, dtype=torch.int8, device=w.device), q.fp16_outliers,
+                                  torch.empty(0, dtype=torch.long, device=w.device), q.scale_factors,
+                                  q.original_shape, q.block_size)
+        self.q = slim
+        self.layout = aw.KernelLayout(slim, lay.tiles, lay.row_ptr, lay.col, lay.n_rows, lay.n_cols)
+        self.module = None
+        if keep_module:
+            self.module = ab.QuantizedLinear(slim, None)
+            self.module._kernel_layout = self.layout
+
+    def forward(self, x, force=None):
+        from atlasinfer_b200.integration import atlas_wrappers as aw
+        return aw.quantized_linear_forward(x, self.q, self.layout, None, force)
+
+
+def build_model(linears, layers, gen, sigma, rows_slice=None, keep_module=False):
+    """`layers` x the given linears; rows_slice=(rank, world) keeps this rank's output rows."""
+    out = []
+    for _ in range(layers):
+        for name, n, k in linears:
+            if rows_slice is not None:
+                r, wsz = rows_slice
+                n = n // wsz
+            w = synth_weight(n, k, gen, sigma)
+            out.append((name, Linear(w, keep_module)))
+            del w
+    return out
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        # samples under load: the upper half of the observed clocks
+        busy = sm[len(sm) // 2:] if sm else []
+        med = busy[len(busy) // 2] if busy else None
+        return dict(sm_mhz=med, sm_max_mhz=max(smax) if smax else None, reasons=sorted(reasons), samples=len(sm))
+
+
+# ----------------------------------------------------------------------------- timing helpers
+def time_steps(fn, steps, warmup, barrier=None):
+    """Device time of `steps` calls of fn after `warmup` untimed ones (CUDA events on the current stream)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    return ev[0].elapsed_time(ev[steps]) / 1e3  # seconds
+
+
+def capture_graph(fn):
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+# ----------------------------------------------------------------------------- measurements
+def measure_gemv(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16):
+    """(bytes per step, seconds for `steps`, launches per step) of a graph-replayed decode pass."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(7 + m)
+    xs = {k: torch.randn(m, k, generator=gen, device=dev).to(dtype) for k in {l.k for _, l in model}}
+    outs = []
+
+    def one_pass():
+        outs.clear()
+        for _, lin in model:
+            outs.append(lin.forward(xs[lin.k], "gemv"))
+
+    if NO_GRAPH:
+        secs = time_steps(one_pass, steps, warmup, barrier)
+    else:
+        graph = capture_graph(one_pass)
+        secs = time_steps(graph.replay, steps, warmup, barrier)
+    nbytes = sum(linear_bytes(l.n, l.k, l.n_out, m) for _, l in model)
+    return nbytes, secs, len(model)
+
+
+def measure_e2e(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16):
+    """The decode pass through QuantizedLinear.forward with host-resident activations."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator().manual_seed(11)
+    hx = {k: torch.randn(m, k, generator=gen).to(dtype).pin_memory() for k in {l.k for _, l in model}}
+    hy = {n: torch.empty(m, n, dtype=dtype).pin_memory() for n in {l.n for _, l in model}}
+
+    def one_pass():
+        for _, lin in model:
+            x = hx[lin.k].to(dev, non_blocking=True)
+            y = lin.module(x)
+            hy[lin.n].copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller holds y on the host
+
+    secs = time_steps(one_pass, steps, warmup, barrier)
+    h2d = sum(m * l.k * 2 for _, l in model)
+    d2h = sum(m * l.n * 2 for _, l in model)
+    nbytes = sum(linear_bytes(l.n, l.k, l.n_out, m) for _, l in model)
+    return nbytes, secs, h2d, d2h
+
+
+def measure_gemm(steps, warmup):
+    """Prefill GEMM TFLOP/s: 2048 tokens against 11008x4096 and 4096x4096 (config 4)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(99)
+    res = {}
+    for n, k in ((11008, 4096), (4096, 4096)):
+        # several distinct weights so that consecutive calls do not re-read one from L2
+        reps = 4
+        lins = [Linear(synth_weight(n, k, gen)) for _ in range(reps)]
+        x = torch.randn(2048, k, generator=gen, device=dev).to(torch.bfloat16)
+        ch = torch.randperm(k, generator=gen, device=dev)[: max(1, round(0.005 * k))]
+        x[:, ch] *= 20
+
+        def one():
+            for l in lins:
+                l.forward(x, "gemm")
+
+        secs = time_steps(one, steps, warmup)
+        res[f"{n}x{k}"] = 2.0 * 2048 * n * k * reps * steps / secs / 1e12
+        del lins
+    return res
+
+
+def measure_quantize(steps, warmup):
+    """Quantize GB/s on the 7B shapes: algorithmic bytes = 2 B read + codes + scales + 10 B per outlier."""
+    import atlasinfer_b200 as ab
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(5)
+    ws = [synth_weight(n, k, gen) for n, k in ((11008, 4096), (4096, 11008), (4096, 4096), (11008, 4096))]
+    nbytes = 0
+    for w in ws:
+        q = ab.quantize_tensor(w)
+        n_out = q.fp16_outliers.numel()
+        nbytes += 2 * w.numel() + (w.numel() - n_out) + (w.numel() // BLOCK) * 2 + n_out * 10
+
+    def one():
+        for w in ws:
+            ab.quantize_tensor(w)
+
+    secs = time_steps(one, steps, warmup)
+    return nbytes * steps / secs / 1e9
+
+
+def cpu_linear_pass(linears, m, threads_note=True):
+    """One pass of the CPU oracle port over `linears` [(n, k)]: dequantize + fp32 product per call.
+    Returns (algorithmic bytes, seconds).  Weights are quantized (untimed) by the oracle first."""
+    from oracle import atlas_oracle as O
+    gen = torch.Generator().manual_seed(3)
+    prepared = []
+    for n, k in linears:
+        w = (torch.randn(n, k, generator=gen) * 0.02)
+        cnt = round(1e-3 * n * k)
+        w.view(-1)[torch.randint(0, n * k, (cnt,), generator=gen)] = 0.3
+        q = O.quantize(w.half())
+        x = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+        prepared.append((q, x, linear_bytes(n, k, q.fp16_outliers.numel(), m)))
+    t0 = time.perf_counter()
+    for q, x, _ in prepared:
+        O.linear(x, O.dequantize(q))
+    return sum(b for _, _, b in prepared), time.perf_counter() - t0
+
+
+# ----------------------------------------------------------------------------- arms
+def run_reference(args, rank, world):
+    """CPU arm: the oracle port of the quantized linear forward on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    from oracle import atlas_oracle as O
+    O.build()
+    sample = [(4096, 4096), (11008, 4096), (4096, 11008)]
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_linear_pass(sample[:1], 1)
+    t_all, b_all = 0.0, 0
+    for _ in range(args.steps):
+        b, t = cpu_linear_pass(sample, 1)
+        t_all += t
+        b_all += b
+    val = b_all / t_all / 1e9
+    cores = O.threads()
+    desc = ("per step: q_proj 4096x4096 + gate_proj 11008x4096 + down_proj 4096x11008 at batch 1, "
+            "dequantize_tensor + fp32 matmul per call (CPU oracle port, OpenMP)")
+    line = dict(
+        impl="reference", metric="dequant_gemv_hbm_gbs", value=val, unit="GB/s", n_gpus=args.gpus,
+        steps=args.steps, warmup=args.warmup, ms_per_step=t_all / args.steps * 1e3, higher_is_better=True,
+        scaling="weak", vs_baseline=None, dtype="int8 codes x fp16 scales, fp32 accumulate", data="synthetic",
+        config=workload_config(1), gpu_launches=0,
+        cpu_baseline=dict(value=val, unit="GB/s", cores=cores, kind="port", sample=desc),
+        e2e=dict(value=val, unit="GB/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(m):
+    return dict(workload="llama2-7b decode linears: 32 layers x (q,k,v,o 4096x4096; gate,up 11008x4096; "
+                         "down 4096x11008), block 128, z 3.0, weights N(0,0.02)+0.1% outliers",
+                batch=m, activations="bf16 N(0,1)", l2="each step streams 6.7 GB of weights (>> 126 MB L2)",
+                launch="one kernel per linear, step replayed from a CUDA graph")
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    from atlasinfer_b200 import _capi
+    _capi.load()  # fail here, loudly, if the CUDA library is missing
+    barrier = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        barrier = dist.barrier
+    pk = peaks()
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    t_setup = time.perf_counter()
+    model = build_model(LLAMA7B_LINEARS, args.layers, gen, 0.02, keep_module=True)
+    torch.cuda.synchronize()
+    t_setup = time.perf_counter() - t_setup
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    nbytes, secs, launches = measure_gemv(model, 1, args.steps, args.warmup, barrier)
+    clocks = sampler.stop()
+    e_bytes, e_secs, h2d, d2h = measure_e2e(model, 1, args.steps, args.warmup, barrier)
+
+    def allmax(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    secs, e_secs = allmax(secs), allmax(e_secs)
+    value = world * nbytes * args.steps / secs / 1e9
+    e2e_value = world * e_bytes * args.steps / e_secs / 1e9
+    per_gpu = value / world
+
+    extra = {}
+    if rank == 0 and not args.headline_only:
+        for m in (4, 16):
+            b, s, _ = measure_gemv(model, m, max(2, args.steps // 2), 3)
+            extra[f"gemv_m{m}_gbs"] = b * max(2, args.steps // 2) / s / 1e9
+    del model
+    torch.cuda.empty_cache()
+    if rank == 0 and not args.headline_only:
+        try:
+            extra["prefill_gemm_tflops"] = measure_gemm(max(2, args.steps // 4), 3)
+            extra["quantize_gbs"] = measure_quantize(max(2, args.steps // 4), 3)
+        except Exception as e:  # noqa: BLE001 - secondary figures must not lose the headline line
+            extra["error"] = repr(e)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        from oracle import atlas_oracle as O
+        O.build()
+        b, t = cpu_linear_pass([(4096, 4096), (11008, 4096)], 1)
+        cpu = dict(value=b / t / 1e9, unit="GB/s", cores=O.threads(), kind="port",
+                   sample="q_proj 4096x4096 + gate_proj 11008x4096 at batch 1, dequantize + fp32 matmul "
+                          "per call through the CPU oracle port (OpenMP)")
+
+    if rank == 0:
+        line = dict(
+            metric="dequant_gemv_hbm_gbs", value=value, unit="GB/s", n_gpus=world, steps=args.steps,
+            warmup=args.warmup, ms_per_step=secs / args.steps * 1e3, higher_is_better=True, scaling="weak",
+            vs_baseline=None, dtype="int8 codes x fp16 scales -> fp16 MMA, fp32 accumulate", data="synthetic",
+            config=dict(workload_config(1), layers=args.layers), clocks=clocks,
+            e2e=dict(value=e2e_value, unit="GB/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+            gpu_launches=launches * args.steps,
+            roofline=dict(bound="hbm", achieved=per_gpu, peak=pk["hbm"], unit="GB/s", frac=per_gpu / pk["hbm"],
+                          traffic=None, peak_source=pk["source"], kernel="gemv_kernel",
+                          frac_of_nominal_8tbs=per_gpu / 8000.0),
+            cpu_baseline=cpu, extra=extra, setup_s=t_setup)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--headline-only", action="store_true", help="skip the secondary figures")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", type=int, default=LLAMA7B["layers"],
+                    help="decoder layers in the pass (default: the full 32; smaller only for profiler captures)")
+    ap.add_argument("--no-graph", action="store_true", help="launch the pass directly instead of replaying a graph")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    global NO_GRAPH
+    NO_GRAPH = args.no_graph
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()
