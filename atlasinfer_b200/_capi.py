@@ -60,14 +60,14 @@ def load() -> ctypes.CDLL:
     L.atlas_tiles_bytes.restype = sz
     L.atlas_tiles_bytes.argtypes = [i64, i64]
     L.atlas_repack.restype = i32
-    L.atlas_repack.argtypes = [vp, i64, vp, i64, i64, i64, i32, vp, vp, vp, vp]
+    L.atlas_repack.argtypes = [vp, i64, vp, vp, i64, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp]
     lin = [vp, i32, i64, i64, vp, vp, vp, vp, vp, i64, i64, i32, vp, vp, i64]
     L.atlas_qlinear_gemv.restype = i32
-    L.atlas_qlinear_gemv.argtypes = lin + [vp]
+    L.atlas_qlinear_gemv.argtypes = lin + [vp, vp]
     L.atlas_qlinear_gemm_workspace_bytes.restype = sz
     L.atlas_qlinear_gemm_workspace_bytes.argtypes = [i64, i64]
     L.atlas_qlinear_gemm.restype = i32
-    L.atlas_qlinear_gemm.argtypes = lin + [vp, sz, vp]
+    L.atlas_qlinear_gemm.argtypes = lin + [vp, sz, vp, vp]
     _lib = L
     return L
 

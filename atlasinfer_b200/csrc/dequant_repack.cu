@@ -84,12 +84,12 @@ __device__ __forceinline__ int64_t tile_offset(int64_t row, int64_t col, int64_t
 
 __global__ void __launch_bounds__(DQ_THREADS)
 repack_kernel(const int8_t *codes, int64_t n_codes, const int64_t *oidx, int64_t n_out, int64_t n_rows,
-              int64_t n_cols, uint8_t *tiles, int32_t *ocol) {
+              int64_t n_cols, uint8_t *tiles) {
     const int64_t k_tiles = n_cols >> 6;
     walk_span(codes, n_codes, oidx, n_out, n_rows * n_cols, [&](int64_t p, bool is_out, int64_t k, int8_t code) {
         const int64_t row = p / n_cols, col = p - row * n_cols;
         tiles[tile_offset(row, col, k_tiles)] = (uint8_t)((int)code + 128);
-        if (is_out) ocol[k] = (int32_t)col;
+        (void)is_out; (void)k;
     });
 }
 
@@ -108,6 +108,73 @@ __global__ void __launch_bounds__(DQ_THREADS)
 row_ptr_kernel(const int64_t *oidx, int64_t n_out, int64_t n_rows, int64_t n_cols, int32_t *row_ptr) {
     const int64_t r = (int64_t)blockIdx.x * DQ_THREADS + threadIdx.x;
     if (r <= n_rows) row_ptr[r] = (int32_t)lower_bound_i64(oidx, n_out, r * n_cols);
+}
+
+// Scales transposed per 128-row tile: [row/128][block][row%128], so that the scales of a
+// run of rows for one K block are contiguous.
+__global__ void __launch_bounds__(DQ_THREADS)
+scales_tile_kernel(const uint16_t *scales, int64_t n_rows, int64_t n_rows_padded, int64_t blocks_per_row,
+                   uint16_t *scales_t) {
+    const int64_t total = n_rows_padded * blocks_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * DQ_THREADS + threadIdx.x; i < total; i += (int64_t)gridDim.x * DQ_THREADS) {
+        const int64_t rt = i / (blocks_per_row * 128), rem = i - rt * blocks_per_row * 128;
+        const int64_t kb = rem >> 7, r = rem & 127;
+        const int64_t row = rt * 128 + r;
+        scales_t[i] = row < n_rows ? scales[row * blocks_per_row + kb] : (uint16_t)0;
+    }
+}
+
+// Outliers regrouped by 16-row strip and sorted by column inside a strip.  Entry = row%16 << 24 |
+// column.  The position of an outlier is found by counting, over the 16 row lists of its strip
+// (each sorted by column already), the entries that precede it: deterministic, no atomics.
+__global__ void __launch_bounds__(DQ_THREADS)
+strip_sort_kernel(const int64_t *oidx, const uint16_t *ovals, int64_t n_out, int64_t n_rows, int64_t n_cols,
+                  const int32_t *row_ptr, uint32_t *entries, uint16_t *vals_sorted) {
+    const int64_t i = (int64_t)blockIdx.x * DQ_THREADS + threadIdx.x;
+    if (i >= n_out) return;
+    const int64_t idx = oidx[i];
+    const int64_t row = idx / n_cols, col = idx - row * n_cols;
+    const int64_t r0 = row & ~(int64_t)15;
+    int rank = 0;
+    for (int64_t r = r0; r < r0 + 16 && r < n_rows; ++r) {
+        // entries of row r with column < col (rows above) or <= col (rows below or equal: ties keep row order)
+        const int64_t key = r * n_cols + col + (r < row ? 1 : 0);
+        int lo = row_ptr[r], hi = row_ptr[r + 1];
+        const int base = lo;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (oidx[mid] < key) lo = mid + 1; else hi = mid;
+        }
+        rank += lo - base;
+    }
+    const int pos = row_ptr[r0] + rank;
+    entries[pos] = (uint32_t)(row & 15) << 24 | (uint32_t)col;
+    vals_sorted[pos] = ovals[i];
+}
+
+// chunk_ptr[strip][c] = first entry of the strip with column >= 256 * c (c = 0 .. n_chunks,
+// n_chunks = ceil(n_cols / 256); the last boundary is the end of the strip).
+__global__ void __launch_bounds__(DQ_THREADS)
+chunk_ptr_kernel(const int64_t *oidx, int64_t n_rows, int64_t n_cols, const int32_t *row_ptr, int64_t n_strips,
+                 int n_chunks, int32_t *chunk_ptr) {
+    const int64_t i = (int64_t)blockIdx.x * DQ_THREADS + threadIdx.x;
+    if (i >= n_strips * (n_chunks + 1)) return;
+    const int64_t strip = i / (n_chunks + 1);
+    const int c = (int)(i - strip * (n_chunks + 1));
+    const int64_t r0 = strip * 16;
+    if (r0 >= n_rows) { chunk_ptr[i] = row_ptr[n_rows]; return; }
+    int count = 0;
+    for (int64_t r = r0; r < r0 + 16 && r < n_rows; ++r) {
+        const int64_t key = r * n_cols + min((int64_t)c * 256, n_cols);
+        int lo = row_ptr[r], hi = row_ptr[r + 1];
+        const int base = lo;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (oidx[mid] < key) lo = mid + 1; else hi = mid;
+        }
+        count += lo - base;
+    }
+    chunk_ptr[i] = row_ptr[r0] + count;
 }
 
 }  // namespace
@@ -144,9 +211,10 @@ size_t atlas_tiles_bytes(int64_t n_rows, int64_t n_cols) {
     return (size_t)(atlas::ceil_div_i64(n_rows, 128) * 128 * n_cols);
 }
 
-int atlas_repack(const int8_t *codes, int64_t n_codes, const int64_t *outlier_idx, int64_t n_outliers,
-                 int64_t n_rows, int64_t n_cols, int block_size, uint8_t *tiles, int32_t *outlier_row_ptr,
-                 int32_t *outlier_col, void *stream) {
+int atlas_repack(const int8_t *codes, int64_t n_codes, const void *outlier_vals, const int64_t *outlier_idx,
+                 int64_t n_outliers, const void *scales, int64_t n_rows, int64_t n_cols, int block_size,
+                 uint8_t *tiles, void *scales_tiled, int32_t *outlier_row_ptr, int32_t *outlier_chunk_ptr,
+                 uint32_t *outlier_entries, void *outlier_vals_sorted, void *stream) {
     using namespace atlas;
     clear_error();
     ATLAS_RETURN_IF(n_rows <= 0 || n_cols <= 0 || n_codes < 0 || n_outliers < 0 || block_size < 1,
@@ -155,12 +223,14 @@ int atlas_repack(const int8_t *codes, int64_t n_codes, const int64_t *outlier_id
                     ATLAS_ERR_UNSUPPORTED,
                     "atlas_repack: needs n_cols %% 64 == 0, block_size %% 16 == 0 and n_cols %% block_size == 0 "
                     "(got n_cols=%lld block_size=%d)", (long long)n_cols, block_size);
-    ATLAS_RETURN_IF(n_cols > 0x7fffffff || n_outliers > 0x7fffffff, ATLAS_ERR_UNSUPPORTED,
-                    "atlas_repack: sizes beyond int32");
+    ATLAS_RETURN_IF(n_cols >= (1 << 24) || n_outliers > 0x7fffffff, ATLAS_ERR_UNSUPPORTED,
+                    "atlas_repack: n_cols >= 2^24 or more than 2^31 outliers");
     ATLAS_RETURN_IF(n_codes + n_outliers != n_rows * n_cols, ATLAS_ERR_BAD_ARGUMENT,
                     "atlas_repack: %lld codes + %lld outliers do not cover %lld x %lld",
                     (long long)n_codes, (long long)n_outliers, (long long)n_rows, (long long)n_cols);
-    ATLAS_RETURN_IF(!tiles || !outlier_row_ptr || (n_codes && !codes) || (n_outliers && (!outlier_idx || !outlier_col)),
+    ATLAS_RETURN_IF(!tiles || !scales || !scales_tiled || !outlier_row_ptr || !outlier_chunk_ptr ||
+                        (n_codes && !codes) ||
+                        (n_outliers && (!outlier_idx || !outlier_vals || !outlier_entries || !outlier_vals_sorted)),
                     ATLAS_ERR_BAD_ARGUMENT, "atlas_repack: null buffer");
     int rc = check_device();
     if (rc) return rc;
@@ -169,7 +239,7 @@ int atlas_repack(const int8_t *codes, int64_t n_codes, const int64_t *outlier_id
     const int64_t grid = ceil_div_i64(numel, DQ_SPAN);
     ATLAS_RETURN_IF(grid > 0x7fffffff, ATLAS_ERR_UNSUPPORTED, "atlas_repack: tensor too large");
     repack_kernel<<<(unsigned)grid, DQ_THREADS, 0, st>>>(codes, n_codes, outlier_idx, n_outliers, n_rows,
-                                                         n_cols, tiles, outlier_col);
+                                                         n_cols, tiles);
     rc = check_cuda(cudaGetLastError(), "repack_kernel launch");
     if (rc) return rc;
     const int64_t rows_padded = ceil_div_i64(n_rows, 128) * 128;
@@ -180,9 +250,30 @@ int atlas_repack(const int8_t *codes, int64_t n_codes, const int64_t *outlier_id
         rc = check_cuda(cudaGetLastError(), "repack_pad_kernel launch");
         if (rc) return rc;
     }
+    const int64_t bpr = n_cols / block_size;
+    {
+        const int64_t g = ceil_div_i64(rows_padded * bpr, DQ_THREADS);
+        scales_tile_kernel<<<(unsigned)(g < 8192 ? g : 8192), DQ_THREADS, 0, st>>>(
+            (const uint16_t *)scales, n_rows, rows_padded, bpr, (uint16_t *)scales_tiled);
+        rc = check_cuda(cudaGetLastError(), "scales_tile_kernel launch");
+        if (rc) return rc;
+    }
     row_ptr_kernel<<<(unsigned)ceil_div_i64(n_rows + 1, DQ_THREADS), DQ_THREADS, 0, st>>>(
         outlier_idx, n_outliers, n_rows, n_cols, outlier_row_ptr);
-    return check_cuda(cudaGetLastError(), "row_ptr_kernel launch");
+    rc = check_cuda(cudaGetLastError(), "row_ptr_kernel launch");
+    if (rc) return rc;
+    if (n_outliers > 0) {
+        strip_sort_kernel<<<(unsigned)ceil_div_i64(n_outliers, DQ_THREADS), DQ_THREADS, 0, st>>>(
+            outlier_idx, (const uint16_t *)outlier_vals, n_outliers, n_rows, n_cols, outlier_row_ptr,
+            outlier_entries, (uint16_t *)outlier_vals_sorted);
+        rc = check_cuda(cudaGetLastError(), "strip_sort_kernel launch");
+        if (rc) return rc;
+    }
+    const int64_t n_strips = rows_padded / 16;
+    const int n_chunks = (int)ceil_div_i64(n_cols, 256);
+    chunk_ptr_kernel<<<(unsigned)ceil_div_i64(n_strips * (n_chunks + 1), DQ_THREADS), DQ_THREADS, 0, st>>>(
+        outlier_idx, n_rows, n_cols, outlier_row_ptr, n_strips, n_chunks, outlier_chunk_ptr);
+    return check_cuda(cudaGetLastError(), "chunk_ptr_kernel launch");
 }
 
 }  // extern "C"

@@ -1,18 +1,477 @@
-// Prefill-time quantized linear (m >= 128).  Placeholder while the tcgen05 kernel is
-// brought up: routes through the streaming kernel in groups of 32 rows (correct, re-reads W).
+// Prefill-time quantized linear: y[m][n] = sum_k x[m][k] * W[n][k] + bias[n], m >= 128.
+//
+// Replaces the dequantize-then-F.linear of QuantizedLinear.forward
+// (integration/atlas_wrappers.py:56,67) for prompt-sized batches.  The fp16
+// weight the reference materialises (adaptive_quantizer.py:216:
+// fp16(fp16(code) * scale), outliers patched in at :221-229) is rebuilt here
+// tile by tile in shared memory and consumed at once by the 5th-generation
+// tensor cores, so it never exists in global memory.
+//
+// One CTA computes a 128 (output features) x 256 (tokens) tile:
+//   warp 0      producer: per 64-wide K step a 1-D bulk copy of the 8 KB code
+//               tile (the tile-major layout makes it contiguous) and a 2-D TMA
+//               load of the 256 x 64 fp16 activation tile (128-byte swizzle),
+//               both completing on the stage's `full` mbarrier
+//   warps 2-5   dequantizers: codes -> fp16 A-operand tile in the canonical
+//               K-major 128-byte-swizzled layout, outliers of the tile written
+//               over their (zero-coded) slots from the strip-sorted side-table, then
+//               fence.proxy.async + arrive on `a_ready`
+//   warp 1      one thread issues tcgen05.mma (M=128, N=256, K=16, fp16 in,
+//               fp32 accumulate in TMEM) four times per stage and commits the
+//               stage's `empty` mbarrier; after the last step it commits
+//               `acc_full`
+//   warps 2-5   epilogue: tcgen05.ld of their TMEM lane quarter, + bias,
+//               convert, store y
+// Every mbarrier wait is bounded; if one runs out the CTA sets the caller's status word,
+// skips the rest of its work, frees its TMEM and returns.
+//
+// bf16 activations are first converted to fp16 into the workspace (the MMA
+// takes both operands as fp16; |x| > 65504 saturates).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
+namespace atlas {
+namespace {
+
+constexpr int GM_THREADS = 192;
+constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
+constexpr int GM_BN = 256;  // tokens per CTA = UMMA N
+constexpr int GM_BK = 64;   // K per pipeline stage (one 128-byte swizzle row of fp16)
+constexpr int GM_STAGES = 4;
+constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2;  // 16 KB fp16 weight tile
+constexpr uint32_t B_BYTES = GM_BN * GM_BK * 2;  // 32 KB fp16 activation tile
+constexpr uint32_t C_BYTES = GM_BM * GM_BK;      // 8 KB code tile
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + C_BYTES;
+constexpr uint32_t GM_SMEM = GM_STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t TMEM_COLS = 256;
+constexpr int GM_SPIN_LIMIT = 1 << 20;
+
+// ---- PTX wrappers ----------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the phase did not complete within the spin limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < GM_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand tile, rows of 128 bytes (64 fp16), 128-byte
+// swizzle, 8-row groups 1024 bytes apart.  Fields: start address >> 4 at bit 0, leading byte
+// offset >> 4 at bit 16 (not used by swizzled K-major layouts; 1), stride byte offset >> 4 at bit
+// 32, descriptor version 1 at bit 46, swizzle mode 2 (128 B) at bit 61.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor, kind::f16: D fp32 (1 at bit 4), A and B fp16 (0 at bits 7 and 10),
+// both K-major (0 at bits 15, 16), N >> 3 at bit 17, M >> 4 at bit 24.
+constexpr uint32_t GM_IDESC = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
+
+// Four biased codes -> two half2 of fp16(fp16(code) * scale), as in the streaming kernel.
+__device__ __forceinline__ void dequant4(uint32_t w, __half2 scale2, uint32_t &lo, uint32_t &hi) {
+    const uint32_t l = __byte_perm(w, 0x64646464u, 0x5140);
+    const uint32_t h = __byte_perm(w, 0x64646464u, 0x5342);
+    const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
+    __half2 lv = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&l), bias), scale2);
+    __half2 hv = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&h), bias), scale2);
+    lo = *reinterpret_cast<uint32_t *>(&lv);
+    hi = *reinterpret_cast<uint32_t *>(&hv);
+}
+
+struct GemmParams {
+    const uint8_t *tiles;
+    const uint16_t *scales_t;   // [row/128][block][row%128]
+    const int32_t *chunk_ptr;   // [strip][n_chunks + 1]
+    const uint32_t *entries;    // row%16 << 24 | column, strip-major, column-sorted
+    const uint16_t *ovals;      // values in the order of `entries`
+    const uint16_t *bias;
+    void *y;
+    int64_t ldy;
+    int m;
+    int n_rows;
+    int n_cols;
+    int bs;
+    int k_tiles;
+    int n_chunks;
+    int out_bf16;
+    int *error_flag;
+};
+
+__global__ void __launch_bounds__(GM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;          // operand tiles need 1024-byte alignment
+    unsigned char *base_ptr = smem_raw + (base - raw);
+    const uint32_t bars = base + GM_STAGES * STAGE_BYTES;   // mbarriers, 8 bytes each
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto aready_bar = [&](int s) { return bars + 8u * (GM_STAGES + s); };
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * GM_STAGES + s); };
+    const uint32_t accfull_bar = bars + 8u * (3 * GM_STAGES);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + GM_STAGES * STAGE_BYTES + 8 * (3 * GM_STAGES + 1));
+    volatile int *s_abort = reinterpret_cast<volatile int *>(base_ptr + GM_STAGES * STAGE_BYTES + 8 * (3 * GM_STAGES + 1) + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * GM_BM;  // first weight row (output feature) of the tile
+    const int m0 = blockIdx.y * GM_BN;  // first token
+    const int KT = p.k_tiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < GM_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(aready_bar(s), 128);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accfull_bar, 1);
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM allocation is warp-wide; the same warp frees it at the end
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void *)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            const uint8_t *ctile = p.tiles + (size_t)blockIdx.x * KT * C_BYTES;
+            for (int it = 0; it < KT; ++it) {
+                const int s = it % GM_STAGES, round = it / GM_STAGES;
+                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1)) { *s_abort = 1; break; }
+                if (*s_abort) break;
+                const uint32_t st = base + s * STAGE_BYTES;
+                mbar_arrive_expect_tx(full_bar(s), B_BYTES + C_BYTES);
+                tma_load_2d(st + A_BYTES, &x_map, it * GM_BK, m0, full_bar(s));
+                bulk_load_1d(st + A_BYTES + B_BYTES, ctile + (size_t)it * C_BYTES, C_BYTES, full_bar(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < KT && ok; ++it) {
+                const int s = it % GM_STAGES, round = it / GM_STAGES;
+                ok = mbar_wait(aready_bar(s), round & 1) && mbar_wait(full_bar(s), round & 1) && !*s_abort;
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t st = base + s * STAGE_BYTES;
+                const uint64_t da = make_smem_desc(st), db = make_smem_desc(st + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < GM_BK / 16; ++k)  // 32 bytes (16 fp16) further along K per step
+                    umma_f16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), GM_IDESC, (it | k) != 0);
+                umma_commit(empty_bar(s));  // arrives when these MMAs have finished reading the stage
+            }
+            if (!ok) *s_abort = 1;
+            umma_commit(accfull_bar);  // arrives when every MMA issued so far is complete
+        }
+    } else {
+        // ------------------------------ dequantizers, then epilogue ------------------------------
+        const int dw = warp - 2;               // 0..3: strips 2*dw and 2*dw + 1 of the 128-row tile
+        const int g = lane >> 2, tig = lane & 3;
+        const int bpr = p.n_cols / p.bs;
+        const uint16_t *sc_tile = p.scales_t + (int64_t)blockIdx.x * bpr * 128;
+        // rows of the tile this thread rebuilds in every K step: 2 strips x (g, g + 8)
+        int rows[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rows[i] = (2 * dw + (i >> 1)) * 16 + (i & 1) * 8 + g;
+        // outlier cursors of the two strips (lists are sorted by column)
+        int cur[2], end[2];
+        uint32_t nent[2];
+#pragma unroll
+        for (int si = 0; si < 2; ++si) {
+            const int64_t strip = (int64_t)blockIdx.x * 8 + 2 * dw + si;
+            cur[si] = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1));
+            end[si] = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + p.n_chunks);
+            nent[si] = cur[si] < end[si] ? __ldg(p.entries + cur[si]) : 0x00ffffffu;
+        }
+        bool ok = true;
+        for (int it = 0; it < KT && ok; ++it) {
+            const int s = it % GM_STAGES, round = it / GM_STAGES;
+            if (!mbar_wait(full_bar(s), round & 1) || *s_abort) { ok = false; break; }
+            unsigned char *stp = base_ptr + s * STAGE_BYTES;
+            const unsigned char *codes = stp + A_BYTES + B_BYTES;
+            const int k0 = it * GM_BK;
+            const int kb = (k0 + tig * 16) / p.bs;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = rows[i];
+                const uint4 c = *reinterpret_cast<const uint4 *>(codes + (((2 * dw + (i >> 1)) * 2 + (i & 1)) * 32 + lane) * 16);
+                const __half2 sc2 = __half2half2(__ushort_as_half(__ldg(sc_tile + (int64_t)kb * 128 + r)));
+                uint4 o0, o1;
+                dequant4(c.x, sc2, o0.x, o0.y);
+                dequant4(c.y, sc2, o0.z, o0.w);
+                dequant4(c.z, sc2, o1.x, o1.y);
+                dequant4(c.w, sc2, o1.z, o1.w);
+                unsigned char *rowp = stp + (r >> 3) * 1024 + (r & 7) * 128;
+                *reinterpret_cast<uint4 *>(rowp + (((2 * tig) ^ (r & 7)) << 4)) = o0;      // k 16*tig .. +7
+                *reinterpret_cast<uint4 *>(rowp + (((2 * tig + 1) ^ (r & 7)) << 4)) = o1;  // k 16*tig+8 .. +15
+            }
+            // outliers of the two strips inside this K step: the lane that rebuilt the 16-column
+            // segment writes the raw fp16 value over the zero-coded slot (same thread: program order)
+#pragma unroll
+            for (int si = 0; si < 2; ++si) {
+                while ((int)(nent[si] & 0xffffffu) < k0 + GM_BK) {
+                    const int kk = (int)(nent[si] & 0xffffffu) - k0;
+                    const int rs = (int)(nent[si] >> 24);
+                    if ((rs & 7) == g && (kk >> 4) == tig) {
+                        const int r = (2 * dw + si) * 16 + rs;
+                        unsigned char *rowp = stp + (r >> 3) * 1024 + (r & 7) * 128;
+                        *reinterpret_cast<uint16_t *>(rowp + (((kk >> 3) ^ (r & 7)) << 4) + (kk & 7) * 2) = __ldg(p.ovals + cur[si]);
+                    }
+                    ++cur[si];
+                    nent[si] = cur[si] < end[si] ? __ldg(p.entries + cur[si]) : 0x00ffffffu;
+                }
+            }
+            fence_async_smem();  // make the generic-proxy writes visible to the tensor core's reads
+            mbar_arrive(aready_bar(s));
+        }
+        if (!ok) *s_abort = 1;
+
+        // epilogue: TMEM lane = output feature, column = token
+        if (mbar_wait(accfull_bar, 0) && !*s_abort) {
+            tcgen05_fence_after();
+            const int q = warp & 3;  // the TMEM lane quarter this warp may read
+            const int n = n0 + q * 32 + lane;
+            const float bv = (p.bias && n < p.n_rows) ? __half2float(__ushort_as_half(__ldg(p.bias + n))) : 0.f;
+            for (int c = 0; c < GM_BN / 32; ++c) {
+                if (m0 + c * 32 >= p.m) break;  // warp-uniform: no tokens left in this tile
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+                tmem_ld_wait();
+                if (n < p.n_rows) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int m = m0 + c * 32 + j;
+                        if (m < p.m) {
+                            const float f = __uint_as_float(v[j]) + bv;
+                            if (p.out_bf16)
+                                reinterpret_cast<__nv_bfloat16 *>(p.y)[(int64_t)m * p.ldy + n] = __float2bfloat16_rn(f);
+                            else
+                                reinterpret_cast<__half *>(p.y)[(int64_t)m * p.ldy + n] = __float2half_rn(f);
+                        }
+                    }
+                }
+            }
+        } else {
+            *s_abort = 1;
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    if (tid == 0 && *s_abort && p.error_flag) atomicExch(p.error_flag, 1);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// bf16 -> fp16 (saturating) into a dense [m][k] buffer; also used to make strided fp16 rows dense.
+__global__ void __launch_bounds__(256)
+to_f16_kernel(const uint16_t *x, int64_t ldx, int m, int k, int from_bf16, uint16_t *out) {
+    const int64_t total = (int64_t)m * (k >> 1);
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int64_t row = i / (k >> 1), c2 = i - row * (k >> 1);
+        uint32_t v = x[row * ldx + 2 * c2] | (uint32_t)x[row * ldx + 2 * c2 + 1] << 16;
+        if (from_bf16) {
+            float lo = fminf(fmaxf(__uint_as_float(v << 16), -65504.f), 65504.f);
+            float hi = fminf(fmaxf(__uint_as_float(v & 0xffff0000u), -65504.f), 65504.f);
+            __half2 h = __floats2half2_rn(lo, hi);
+            v = *reinterpret_cast<uint32_t *>(&h);
+        }
+        reinterpret_cast<uint32_t *>(out)[i] = v;
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn *out) {
+    static EncodeTiledFn cached = nullptr;
+    if (!cached) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        int rc = check_cuda(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres),
+                            "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+        if (rc) return rc;
+        if (qres != cudaDriverEntryPointSuccess || !fn) {
+            set_error("cuTensorMapEncodeTiled is not available in this driver");
+            return ATLAS_ERR_LAUNCH;
+        }
+        cached = (EncodeTiledFn)fn;
+    }
+    *out = cached;
+    return ATLAS_OK;
+}
+
+constexpr size_t GM_WS_HEADER = 256;  // reserved; the fp16 copy of x follows
+
+}  // namespace
+}  // namespace atlas
+
 extern "C" size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_cols) {
-    (void)m; (void)n_cols;
-    return 0;
+    if (m <= 0 || n_cols <= 0) return atlas::GM_WS_HEADER;
+    return atlas::GM_WS_HEADER + (size_t)m * (size_t)n_cols * 2;
 }
 
 extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
-                                  const void *scales, const int32_t *outlier_row_ptr,
-                                  const int32_t *outlier_col, const void *outlier_vals, int64_t n_rows,
-                                  int64_t n_cols, int block_size, const void *bias, void *y, int64_t ldy,
-                                  void *workspace, size_t workspace_bytes, void *stream) {
-    (void)workspace; (void)workspace_bytes;
-    return atlas_qlinear_gemv(x, dtype, m, ldx, tiles, scales, outlier_row_ptr, outlier_col, outlier_vals,
-                              n_rows, n_cols, block_size, bias, y, ldy, stream);
+                                  const void *scales_tiled, const int32_t *outlier_chunk_ptr,
+                                  const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+                                  int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y,
+                                  int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
+                                  void *stream) {
+    using namespace atlas;
+    clear_error();
+    ATLAS_RETURN_IF(!x || !tiles || !scales_tiled || !outlier_chunk_ptr || !y || !workspace, ATLAS_ERR_BAD_ARGUMENT,
+                    "atlas_qlinear_gemm: null buffer");
+    ATLAS_RETURN_IF(m < 0 || n_rows <= 0 || n_cols <= 0 || ldx < n_cols || ldy < n_rows, ATLAS_ERR_BAD_ARGUMENT,
+                    "atlas_qlinear_gemm: bad size (m=%lld n_rows=%lld n_cols=%lld ldx=%lld ldy=%lld)",
+                    (long long)m, (long long)n_rows, (long long)n_cols, (long long)ldx, (long long)ldy);
+    ATLAS_RETURN_IF(dtype != ATLAS_DTYPE_F16 && dtype != ATLAS_DTYPE_BF16, ATLAS_ERR_BAD_ARGUMENT,
+                    "atlas_qlinear_gemm: dtype %d", dtype);
+    ATLAS_RETURN_IF(n_cols % 64 != 0 || block_size < 16 || block_size % 16 != 0 || n_cols % block_size != 0,
+                    ATLAS_ERR_UNSUPPORTED,
+                    "atlas_qlinear_gemm: needs n_cols %% 64 == 0 and block_size a multiple of 16 dividing n_cols");
+    ATLAS_RETURN_IF(n_rows > 0x7fffff00 || n_cols >= (1 << 24) || m > 0x7fffff00, ATLAS_ERR_UNSUPPORTED,
+                    "atlas_qlinear_gemm: too large");
+    ATLAS_RETURN_IF(((uintptr_t)tiles & 15) != 0 || ((uintptr_t)workspace & 255) != 0, ATLAS_ERR_BAD_ARGUMENT,
+                    "atlas_qlinear_gemm: tiles must be 16-byte and workspace 256-byte aligned");
+    const size_t need = atlas_qlinear_gemm_workspace_bytes(m, n_cols);
+    ATLAS_RETURN_IF(workspace_bytes < need, ATLAS_ERR_CAPACITY,
+                    "atlas_qlinear_gemm: workspace holds %zu bytes, %zu needed", workspace_bytes, need);
+    int rc = check_device();
+    if (rc) return rc;
+    if (m == 0) return ATLAS_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+
+
+    // operand B must be fp16 with rows on 16-byte boundaries for the tensor map
+    const void *xb = x;
+    int64_t ldb = ldx;
+    const bool direct = dtype == ATLAS_DTYPE_F16 && ((uintptr_t)x & 15) == 0 && (ldx % 8) == 0;
+    if (!direct) {
+        uint16_t *xf = (uint16_t *)((char *)workspace + GM_WS_HEADER);
+        const int64_t pairs = m * (n_cols / 2);
+        const int64_t blocks = ceil_div_i64(pairs, 256);
+        to_f16_kernel<<<(unsigned)(blocks < 65535 ? blocks : 65535), 256, 0, st>>>(
+            (const uint16_t *)x, ldx, (int)m, (int)n_cols, dtype == ATLAS_DTYPE_BF16, xf);
+        rc = check_cuda(cudaGetLastError(), "to_f16_kernel launch");
+        if (rc) return rc;
+        xb = xf;
+        ldb = n_cols;
+    }
+
+    EncodeTiledFn encode = nullptr;
+    rc = get_encode_fn(&encode);
+    if (rc) return rc;
+    CUtensorMap x_map;
+    const cuuint64_t gdim[2] = {(cuuint64_t)n_cols, (cuuint64_t)m};
+    const cuuint64_t gstride[1] = {(cuuint64_t)ldb * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)GM_BK, (cuuint32_t)GM_BN};
+    const cuuint32_t estride[2] = {1, 1};
+    CUresult cr = encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(xb), gdim, gstride, box,
+                         estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ATLAS_RETURN_IF(cr != CUDA_SUCCESS, ATLAS_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)cr);
+
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        rc = check_cuda(cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM),
+                        "cudaFuncSetAttribute(gemm smem)");
+        if (rc) return rc;
+        configured_dev = dev;
+    }
+
+    GemmParams p;
+    p.tiles = tiles;
+    p.scales_t = (const uint16_t *)scales_tiled;
+    p.chunk_ptr = outlier_chunk_ptr;
+    p.entries = outlier_entries;
+    p.ovals = (const uint16_t *)outlier_vals_sorted;
+    p.bias = (const uint16_t *)bias;
+    p.y = y;
+    p.ldy = ldy;
+    p.m = (int)m;
+    p.n_rows = (int)n_rows;
+    p.n_cols = (int)n_cols;
+    p.bs = block_size;
+    p.k_tiles = (int)(n_cols / 64);
+    p.n_chunks = (int)ceil_div_i64(n_cols, 256);
+    p.out_bf16 = dtype == ATLAS_DTYPE_BF16;
+    p.error_flag = status;
+    dim3 grid((unsigned)ceil_div_i64(n_rows, GM_BM), (unsigned)ceil_div_i64(m, GM_BN), 1);
+    gemm_kernel<<<grid, GM_THREADS, GM_SMEM, st>>>(x_map, p);
+    return check_cuda(cudaGetLastError(), "gemm_kernel launch");
 }

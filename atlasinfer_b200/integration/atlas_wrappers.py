@@ -28,14 +28,38 @@ _VERBOSE = os.environ.get("ATLAS_VERBOSE", "0") not in ("", "0")
 
 
 class KernelLayout(NamedTuple):
-    """Device-resident kernel image of one quantized [N, K] weight."""
+    """Device-resident kernel image of one quantized [N, K] weight (written by atlas_repack)."""
 
     source: object                 # the QuantizedTensor it was built from (identity-checked)
     tiles: torch.Tensor            # uint8, tile-major dense codes + 128
-    row_ptr: torch.Tensor          # int32 [N + 1], CSR over the outlier streams
-    col: torch.Tensor              # int32 [n_outliers]
+    scales_tiled: torch.Tensor     # fp16, [N/128][K/block][128]
+    row_ptr: torch.Tensor          # int32 [N + 1], CSR over the canonical outlier streams
+    chunk_ptr: torch.Tensor        # int32 [N_padded/16][ceil(K/256) + 1]
+    entries: torch.Tensor          # int32 (row%16 << 24 | col), strip-major, column-sorted
+    vals_sorted: torch.Tensor      # fp16 outlier values in the order of `entries`
     n_rows: int
     n_cols: int
+    block_size: int
+
+
+_status_words = {}
+
+
+def status_word(dev: torch.device) -> torch.Tensor:
+    """The device int32 kernels set non-zero when a bounded wait ran out (one per device)."""
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    t = _status_words.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status_words[key] = t
+    return t
+
+
+def check_status(dev: torch.device) -> None:
+    """Synchronise and raise if any kernel on ``dev`` reported a timed-out wait."""
+    if int(status_word(dev).item()) != 0:
+        status_word(dev).zero_()
+        raise _capi.AtlasError(_capi.ERR_TIMEOUT, "a quantized-linear kernel gave up on a bounded wait")
 
 
 def kernel_layout_supported(shape, block_size: int) -> Optional[str]:
@@ -59,20 +83,27 @@ def build_kernel_layout(q: QuantizedTensor) -> KernelLayout:
     dev = q.fp8_data.device
     n, k = int(q.original_shape[0]), int(q.original_shape[1])
     n_out = q.outlier_indices.numel()
+    bs = int(q.block_size)
+    n_pad = (n + 127) // 128 * 128
     with torch.cuda.device(dev):
         tiles = torch.empty(int(L.atlas_tiles_bytes(n, k)), dtype=torch.uint8, device=dev)
+        scales_tiled = torch.empty(n_pad * (k // bs), dtype=torch.float16, device=dev)
         row_ptr = torch.empty(n + 1, dtype=torch.int32, device=dev)
-        col = torch.empty(n_out, dtype=torch.int32, device=dev)
+        chunk_ptr = torch.empty((n_pad // 16) * ((k + 255) // 256 + 1), dtype=torch.int32, device=dev)
+        entries = torch.empty(n_out, dtype=torch.int32, device=dev)
+        vals_sorted = torch.empty(n_out, dtype=torch.float16, device=dev)
         codes, oidx = q.fp8_data.contiguous(), q.outlier_indices.contiguous()
-        status = L.atlas_repack(_capi.ptr(codes), codes.numel(), _capi.ptr(oidx), n_out, n, k,
-                                int(q.block_size), tiles.data_ptr(), row_ptr.data_ptr(),
-                                _capi.ptr(col), _capi.stream_ptr(dev))
+        ovals, scales = q.fp16_outliers.contiguous(), q.scale_factors.contiguous()
+        status = L.atlas_repack(_capi.ptr(codes), codes.numel(), _capi.ptr(ovals), _capi.ptr(oidx), n_out,
+                                scales.data_ptr(), n, k, bs, tiles.data_ptr(), scales_tiled.data_ptr(),
+                                row_ptr.data_ptr(), chunk_ptr.data_ptr(), _capi.ptr(entries),
+                                _capi.ptr(vals_sorted), _capi.stream_ptr(dev))
     _capi.check(status, "atlas_repack")
-    return KernelLayout(q, tiles, row_ptr, col, n, k)
+    return KernelLayout(q, tiles, scales_tiled, row_ptr, chunk_ptr, entries, vals_sorted, n, k, bs)
 
 
-def quantized_linear_forward(x: torch.Tensor, q: QuantizedTensor, layout: KernelLayout,
-                             bias: Optional[torch.Tensor], force: Optional[str] = None) -> torch.Tensor:
+def quantized_linear_forward(x: torch.Tensor, layout: KernelLayout, bias: Optional[torch.Tensor],
+                             force: Optional[str] = None) -> torch.Tensor:
     """``x @ W^T + bias`` on CUDA tensors through the C ABI.  ``force``: "gemv" / "gemm"."""
     L = _capi.load()
     dev = x.device
@@ -98,18 +129,18 @@ def quantized_linear_forward(x: torch.Tensor, q: QuantizedTensor, layout: Kernel
         b = bias if bias.dtype == torch.float16 else bias.to(torch.float16)
         b = b.contiguous()
     use_gemv = (m <= GEMV_MAX_ROWS) if force is None else (force == "gemv")
-    ovals = q.fp16_outliers
-    args = [x2.data_ptr(), dtype, m, ldx, layout.tiles.data_ptr(), q.scale_factors.data_ptr(),
-            layout.row_ptr.data_ptr(), _capi.ptr(layout.col), _capi.ptr(ovals), n, k,
-            int(q.block_size), _capi.ptr(b), y.data_ptr(), n]
+    args = [x2.data_ptr(), dtype, m, ldx, layout.tiles.data_ptr(), layout.scales_tiled.data_ptr(),
+            layout.chunk_ptr.data_ptr(), _capi.ptr(layout.entries), _capi.ptr(layout.vals_sorted), n, k,
+            layout.block_size, _capi.ptr(b), y.data_ptr(), n]
+    flag = status_word(dev).data_ptr()
     with torch.cuda.device(dev):
         if use_gemv:
-            status = L.atlas_qlinear_gemv(*args, _capi.stream_ptr(dev))
+            status = L.atlas_qlinear_gemv(*args, flag, _capi.stream_ptr(dev))
             _capi.check(status, "atlas_qlinear_gemv")
         else:
             ws_bytes = int(L.atlas_qlinear_gemm_workspace_bytes(m, k))
-            ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
-            status = L.atlas_qlinear_gemm(*args, ws.data_ptr(), ws_bytes, _capi.stream_ptr(dev))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            status = L.atlas_qlinear_gemm(*args, ws.data_ptr(), ws_bytes, flag, _capi.stream_ptr(dev))
             _capi.check(status, "atlas_qlinear_gemm")
     return y.view(*x.shape[:-1], n)
 
@@ -149,7 +180,7 @@ class QuantizedLinear(nn.Module):
             bias = self.bias
         layout = self._layout_for(q_tensor)
         xin = x if x.device == compute_device else x.to(compute_device)
-        y = quantized_linear_forward(xin, q_tensor, layout, bias)
+        y = quantized_linear_forward(xin, layout, bias)
         return y if x.device == compute_device else y.to(x.device)
 
     def extra_repr(self) -> str:

@@ -89,12 +89,14 @@ class Linear:
         self.n_out = q.fp16_outliers.numel()
         lay = aw.build_kernel_layout(q)
         torch.cuda.current_stream().synchronize()
-        # the kernels read tiles / CSR / scales / outlier values; the compacted codes are not needed
-        slim = ab.QuantizedTensor(torch.empty(0, dtype=torch.int8, device=w.device), q.fp16_outliers,
-                                  torch.empty(0, dtype=torch.long, device=w.device), q.scale_factors,
+        # the kernels read only the repacked layout; the canonical streams are not needed afterwards
+        slim = ab.QuantizedTensor(torch.empty(0, dtype=torch.int8, device=w.device),
+                                  torch.empty(0, dtype=torch.float16, device=w.device),
+                                  torch.empty(0, dtype=torch.long, device=w.device),
+                                  torch.empty(0, dtype=torch.float16, device=w.device),
                                   q.original_shape, q.block_size)
         self.q = slim
-        self.layout = aw.KernelLayout(slim, lay.tiles, lay.row_ptr, lay.col, lay.n_rows, lay.n_cols)
+        self.layout = lay._replace(source=slim)
         self.module = None
         if keep_module:
             self.module = ab.QuantizedLinear(slim, None)
@@ -102,7 +104,7 @@ class Linear:
 
     def forward(self, x, force=None):
         from atlasinfer_b200.integration import atlas_wrappers as aw
-        return aw.quantized_linear_forward(x, self.q, self.layout, None, force)
+        return aw.quantized_linear_forward(x, self.layout, None, force)
 
 
 def build_model(linears, layers, gen, sigma, rows_slice=None, keep_module=False):

@@ -93,55 +93,71 @@ ATLAS_API int atlas_dequantize(const int8_t *codes, int64_t n_codes, const void 
 /* ---- repack to the kernel layout -----------------------------------------------
  * No counterpart in the reference (which re-derives positions per block at
  * adaptive_quantizer.py:187-212 and caches an fp16 copy).  Expands the
- * compacted code stream of a [n_rows, n_cols] weight into the dense,
- * tile-major layout the linear kernels stream:
+ * compacted streams of a quantized [n_rows, n_cols] weight into the layout the
+ * linear kernels stream:
  *
- *   tiles          atlas_tiles_bytes(n_rows, n_cols) bytes; code + 128 as
- *                  uint8 (outlier positions hold 128, i.e. code 0), ordered
- *                  [row/128][col/64][(row%128)/16][(row%16)/8][(row%8)*4 +
- *                  (col%64)/16][col%16]; rows padded to a multiple of 128
- *   outlier_row_ptr  n_rows + 1 int32: CSR row starts into the outlier streams
- *   outlier_col    n_outliers int32 column of each outlier
+ *   tiles            atlas_tiles_bytes(n_rows, n_cols) bytes; code + 128 as
+ *                    uint8 (outlier positions hold 128, i.e. code 0), ordered
+ *                    [row/128][col/64][(row%128)/16][(row%16)/8][(row%8)*4 +
+ *                    (col%64)/16][col%16]; rows padded to a multiple of 128
+ *   scales_tiled     atlas_tiles_bytes / block_size fp16: the scales ordered
+ *                    [row/128][block][row%128] (0 for padding rows)
+ *   outlier_row_ptr  n_rows + 1 int32: CSR row starts into the canonical
+ *                    outlier streams
+ *   outlier_chunk_ptr  (rows_padded/16) x (ceil(n_cols/256) + 1) int32: for
+ *                    each 16-row strip, the first entry with column >= 256*c
+ *   outlier_entries  n_outliers uint32, (row%16) << 24 | column, grouped by
+ *                    strip and sorted by column within a strip
+ *   outlier_vals_sorted  n_outliers fp16 in the order of outlier_entries
  *
- * Requires n_cols % 64 == 0 and n_cols % block_size == 0 with block_size a
- * multiple of 16 (blocks never straddle rows), else ATLAS_ERR_UNSUPPORTED.
- * Outliers in the padding cannot occur under that condition.
+ * Requires n_cols % 64 == 0, n_cols < 2^24 and n_cols % block_size == 0 with
+ * block_size a multiple of 16 (blocks never straddle rows), else
+ * ATLAS_ERR_UNSUPPORTED.
  */
 ATLAS_API size_t atlas_tiles_bytes(int64_t n_rows, int64_t n_cols);
-ATLAS_API int atlas_repack(const int8_t *codes, int64_t n_codes, const int64_t *outlier_idx,
-                 int64_t n_outliers, int64_t n_rows, int64_t n_cols, int block_size,
-                 uint8_t *tiles, int32_t *outlier_row_ptr, int32_t *outlier_col, void *stream);
+ATLAS_API int atlas_repack(const int8_t *codes, int64_t n_codes, const void *outlier_vals,
+                           const int64_t *outlier_idx, int64_t n_outliers, const void *scales,
+                           int64_t n_rows, int64_t n_cols, int block_size, uint8_t *tiles,
+                           void *scales_tiled, int32_t *outlier_row_ptr, int32_t *outlier_chunk_ptr,
+                           uint32_t *outlier_entries, void *outlier_vals_sorted, void *stream);
 
 /* ---- quantized linear forward ----------------------------------------------------
  * Replaces QuantizedLinear.forward (integration/atlas_wrappers.py:30-74):
  * y[m][n] = sum_k x[m][k] * W[n][k] + bias[n], W being the dequantized weight
- * of dequantize_tensor, never materialised.  x and y share `dtype`
- * (ATLAS_DTYPE_F16 as in the reference, or ATLAS_DTYPE_BF16); bias is fp16 or
- * NULL.  ldx / ldy are row strides in elements.  bf16 activations are used
- * as fp16 inside (|x| > 65504 saturates).
+ * of dequantize_tensor, never materialised.  The weight is given in the
+ * layout atlas_repack writes.  x and y share `dtype` (ATLAS_DTYPE_F16 as in
+ * the reference, or ATLAS_DTYPE_BF16); bias is fp16 or NULL.  ldx / ldy are
+ * row strides in elements.  bf16 activations are used as fp16 inside
+ * (|x| > 65504 saturates).  `status` is a caller-owned device int32 (or NULL)
+ * that a kernel sets non-zero if one of its bounded waits ran out; the library
+ * never clears it.
  *
  * atlas_qlinear_gemv: decode shapes, any m >= 1 (rows are processed in groups
- * of up to 32; intended for m <= 32).  HBM-bound: streams tiles once per
- * group, dequantises in registers and adds the outlier products in the same
- * launch.
+ * of up to 32; intended for m <= 32).  HBM-bound: streams the tiles once per
+ * group through per-warp bulk-copy rings, dequantises in registers and adds
+ * the outlier products in the same launch.  Launched with programmatic
+ * dependent launch: only weights are read before the stream's earlier work
+ * has completed.
  *
  * atlas_qlinear_gemm: prefill shapes (m >= 128 intended, any m >= 1
  * accepted).  Stages tiles through shared memory, dequantises to fp16
  * operand tiles and multiplies with tcgen05 into TMEM accumulators.
- * `workspace` must hold atlas_qlinear_gemm_workspace_bytes(m, n_cols) bytes.
+ * `workspace` must hold atlas_qlinear_gemm_workspace_bytes(m, n_cols) bytes,
+ * 256-byte aligned.
  */
 ATLAS_API int atlas_qlinear_gemv(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
-                       const void *scales, const int32_t *outlier_row_ptr,
-                       const int32_t *outlier_col, const void *outlier_vals, int64_t n_rows,
-                       int64_t n_cols, int block_size, const void *bias, void *y, int64_t ldy,
-                       void *stream);
+                                 const void *scales_tiled, const int32_t *outlier_chunk_ptr,
+                                 const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+                                 int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y,
+                                 int64_t ldy, int32_t *status, void *stream);
 
 ATLAS_API size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_cols);
 ATLAS_API int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
-                       const void *scales, const int32_t *outlier_row_ptr,
-                       const int32_t *outlier_col, const void *outlier_vals, int64_t n_rows,
-                       int64_t n_cols, int block_size, const void *bias, void *y, int64_t ldy,
-                       void *workspace, size_t workspace_bytes, void *stream);
+                                 const void *scales_tiled, const int32_t *outlier_chunk_ptr,
+                                 const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+                                 int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y,
+                                 int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
+                                 void *stream);
 
 #ifdef __cplusplus
 }

@@ -43,7 +43,7 @@ def test_argument_validation_needs_no_gpu(lib):
     assert st == _capi.ERR_UNSUPPORTED and b"block_size" in lib.atlas_last_error()
     st = lib.atlas_quantize(None, -1, 128, 3.0, None, None, None, 0, None, counts, None, 0, None)
     assert st == _capi.ERR_BAD_ARGUMENT
-    st = lib.atlas_repack(None, 0, None, 0, 4, 100, 128, None, None, None, None)
+    st = lib.atlas_repack(None, 0, None, None, 0, None, 4, 100, 128, None, None, None, None, None, None, None)
     assert st == _capi.ERR_UNSUPPORTED
     st = lib.atlas_dequantize(None, 5, None, None, 0, None, 128, 128, None, None)
     assert st == _capi.ERR_BAD_ARGUMENT  # 5 codes + 0 outliers do not cover 128 elements

@@ -132,7 +132,9 @@ def _linear_case(n, k, m, dtype, seed, bias=True, bs=128, sigma=0.02):
 def _run_linear(o, x, b, dev, force=None):
     q = ab.QuantizedTensor(*o).to(dev)
     lay = atlas_wrappers.build_kernel_layout(q)
-    return atlas_wrappers.quantized_linear_forward(x.to(dev), q, lay, None if b is None else b.to(dev), force)
+    y = atlas_wrappers.quantized_linear_forward(x.to(dev), lay, None if b is None else b.to(dev), force)
+    atlas_wrappers.check_status(dev)
+    return y
 
 
 @pytest.mark.parametrize("m", [1, 3, 4, 8, 9, 16, 17, 32, 33, 70])
@@ -161,7 +163,7 @@ def test_gemv_strided_activations_and_outlier_free_weight(cuda_device):
     wide[:, :1024] = x
     q = ab.QuantizedTensor(*o).to(cuda_device)
     lay = atlas_wrappers.build_kernel_layout(q)
-    y = atlas_wrappers.quantized_linear_forward(wide.to(cuda_device)[:, :1024], q, lay, b.to(cuda_device), "gemv")
+    y = atlas_wrappers.quantized_linear_forward(wide.to(cuda_device)[:, :1024], lay, b.to(cuda_device), "gemv")
     assert rel_max_err(y, ref) < LINEAR_TOL
     w = (torch.randn(256, 512, generator=torch.Generator().manual_seed(2)) * 0.02).clamp(-0.04, 0.04).half()
     o2 = O.quantize(w)
