@@ -20,7 +20,7 @@ DTYPE_F16, DTYPE_BF16 = 0, 1
 # every symbol include/atlas_b200.h declares
 EXPORTS = (
     "atlas_version", "atlas_last_error", "atlas_status_string",
-    "atlas_quantize_workspace_bytes", "atlas_quantize", "atlas_dequantize",
+    "atlas_quantize_workspace_bytes", "atlas_quantize", "atlas_quantize_noalloc", "atlas_dequantize",
     "atlas_tiles_bytes", "atlas_repack", "atlas_qlinear_gemv",
     "atlas_qlinear_gemm_workspace_bytes", "atlas_qlinear_gemm",
 )
@@ -55,6 +55,8 @@ def load() -> ctypes.CDLL:
     L.atlas_quantize_workspace_bytes.argtypes = [i64, i32]
     L.atlas_quantize.restype = i32
     L.atlas_quantize.argtypes = [vp, i64, i32, f64, vp, vp, vp, i64, vp, vp, vp, sz, vp]
+    L.atlas_quantize_noalloc.restype = i32
+    L.atlas_quantize_noalloc.argtypes = [vp, i64, i32, f64, vp, vp, vp, i64, vp, vp, vp]
     L.atlas_dequantize.restype = i32
     L.atlas_dequantize.argtypes = [vp, i64, vp, vp, i64, vp, i64, i32, vp, vp]
     L.atlas_tiles_bytes.restype = sz

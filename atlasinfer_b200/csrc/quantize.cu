@@ -20,6 +20,8 @@
 //   code  = int8(clamp(rint(fp16(x / scale)), -127, 127))    (:125-126)
 // The fp64 second moment is a two-pass sum here and a Welford recurrence in
 // ATen; both carry ~1e-16 relative error, far below the fp16 rounding step.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace atlas {
@@ -416,3 +418,65 @@ int atlas_quantize(const void *w, int64_t numel, int block_size, double z_thresh
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Quantize without any allocation by anyone: scratch in a file-scope device array.
+//
+// The look-back needs a tile counter and one status word per tile.  atlas_quantize takes them
+// from a caller-provided workspace; callers that are not allowed to allocate device memory at
+// the point of the call (a pre-allocated arena they may not grow, a fixed-memory serving loop
+// where every cudaMalloc is a synchronisation and a fragmentation risk, a plug-in host that
+// owns the allocator) cannot provide one.  For them the same kernel runs against the static
+// array below, sized for ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS padded elements (64 Mi: 8192 tiles,
+// 64 KB + 16 B).  The array lives in every context that loads this library until it exits.
+constexpr int64_t NOALLOC_MAX_TILES = ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS / atlas::QT_TILE;
+static __device__ __align__(256) unsigned char g_quantize_scratch[16 + 8 * NOALLOC_MAX_TILES];
+
+namespace {
+// In host code `g_quantize_scratch` is only a handle for the symbol, not a device address: the
+// address is looked up once per device, with that device current, and cached.
+int noalloc_scratch_ptr(void **out) {
+    constexpr int kMaxDevices = 64;
+    static void *cache[kMaxDevices] = {nullptr};
+    static std::mutex mu;
+    int dev = -1;
+    int rc = atlas::check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev < 0 || dev >= kMaxDevices) {
+        atlas::set_error("atlas_quantize_noalloc: device ordinal %d outside [0, %d)", dev, kMaxDevices);
+        return ATLAS_ERR_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache[dev] == nullptr) {
+        void *ptr = nullptr;
+        rc = atlas::check_cuda(cudaGetSymbolAddress(&ptr, g_quantize_scratch),
+                               "cudaGetSymbolAddress(g_quantize_scratch)");
+        if (rc) return rc;
+        cache[dev] = ptr;
+    }
+    *out = cache[dev];
+    return ATLAS_OK;
+}
+}  // namespace
+
+extern "C" int atlas_quantize_noalloc(const void *w, int64_t numel, int block_size, double z_threshold,
+                                      int8_t *codes, void *outlier_vals, int64_t *outlier_idx,
+                                      int64_t outlier_capacity, void *scales, int64_t *counts, void *stream) {
+    using namespace atlas;
+    clear_error();
+    ATLAS_RETURN_IF(numel < 0 || block_size <= 0, ATLAS_ERR_BAD_ARGUMENT,
+                    "atlas_quantize_noalloc: negative size or block size");
+    const int64_t padded = ceil_div_i64(numel, block_size) * block_size;
+    ATLAS_RETURN_IF(padded > ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS, ATLAS_ERR_CAPACITY,
+                    "atlas_quantize_noalloc: %lld padded elements exceed the static scratch limit of %lld; "
+                    "use atlas_quantize with a caller-provided workspace",
+                    (long long)padded, (long long)ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS);
+    void *scratch = nullptr;
+    int rc = check_device();
+    if (rc) return rc;
+    rc = noalloc_scratch_ptr(&scratch);
+    if (rc) return rc;
+    // atlas_quantize zeroes the scratch it is given on the stream before the kernel runs
+    return atlas_quantize(w, numel, block_size, z_threshold, codes, outlier_vals, outlier_idx, outlier_capacity,
+                          scales, counts, scratch, sizeof(g_quantize_scratch), stream);
+}

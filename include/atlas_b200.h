@@ -80,6 +80,32 @@ ATLAS_API int atlas_quantize(const void *w, int64_t numel, int block_size, doubl
                    int64_t outlier_capacity, void *scales, int64_t *counts,
                    void *workspace, size_t workspace_bytes, void *stream);
 
+/* ---- quantize for callers that cannot allocate -------------------------------
+ * No counterpart in the reference.  Same computation and outputs as
+ * atlas_quantize, but the look-back scratch lives in a device array inside the
+ * library instead of a caller-provided workspace, and the call performs no
+ * device or host allocation (it issues one cudaMemsetAsync and one kernel).
+ * Meant for hosts that must not allocate where they quantize: a fixed,
+ * pre-reserved memory arena, a serving loop that forbids cudaMalloc after
+ * start-up, a plug-in that does not own the allocator.
+ *
+ *  - limit: ceil(numel / block_size) * block_size <=
+ *    ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS (64 Mi elements, e.g. 8192 x 8192);
+ *    larger inputs return ATLAS_ERR_CAPACITY and must use atlas_quantize.
+ *    The array (64 KB + 16 B) is held by every GPU context that loads the
+ *    library, until the process exits.
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *  - all calls on a device share the array: it is cleared on the stream at the
+ *    start of every call, and two calls whose kernels may overlap on the GPU
+ *    (different streams without ordering) race.  Serialise them.
+ */
+#define ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS ((int64_t)1 << 26)
+ATLAS_API int atlas_quantize_noalloc(const void *w, int64_t numel, int block_size, double z_threshold,
+                                     int8_t *codes, void *outlier_vals, int64_t *outlier_idx,
+                                     int64_t outlier_capacity, void *scales, int64_t *counts,
+                                     void *stream);
+
 /* ---- dequantize ------------------------------------------------------------
  * Replaces dequantize_tensor(quant_data, target_device)
  * (adaptive_quantizer.py:156-251) minus its id()-keyed cache: writes the
