@@ -152,8 +152,7 @@ strip_sort_kernel(const int64_t *oidx, const uint16_t *ovals, int64_t n_out, int
     vals_sorted[pos] = ovals[i];
 }
 
-// chunk_ptr[strip][c] = first entry of the strip with column >= 256 * c (c = 0 .. n_chunks,
-// n_chunks = ceil(n_cols / 256); the last boundary is the end of the strip).
+// chunk_ptr[strip][c] = first entry of the strip with column >= 64 * c (c = 0 .. n_cols / 64).
 __global__ void __launch_bounds__(DQ_THREADS)
 chunk_ptr_kernel(const int64_t *oidx, int64_t n_rows, int64_t n_cols, const int32_t *row_ptr, int64_t n_strips,
                  int n_chunks, int32_t *chunk_ptr) {
@@ -165,7 +164,7 @@ chunk_ptr_kernel(const int64_t *oidx, int64_t n_rows, int64_t n_cols, const int3
     if (r0 >= n_rows) { chunk_ptr[i] = row_ptr[n_rows]; return; }
     int count = 0;
     for (int64_t r = r0; r < r0 + 16 && r < n_rows; ++r) {
-        const int64_t key = r * n_cols + min((int64_t)c * 256, n_cols);
+        const int64_t key = r * n_cols + (int64_t)c * 64;
         int lo = row_ptr[r], hi = row_ptr[r + 1];
         const int base = lo;
         while (lo < hi) {
@@ -270,7 +269,7 @@ int atlas_repack(const int8_t *codes, int64_t n_codes, const void *outlier_vals,
         if (rc) return rc;
     }
     const int64_t n_strips = rows_padded / 16;
-    const int n_chunks = (int)ceil_div_i64(n_cols, 256);
+    const int n_chunks = (int)(n_cols / 64);
     chunk_ptr_kernel<<<(unsigned)ceil_div_i64(n_strips * (n_chunks + 1), DQ_THREADS), DQ_THREADS, 0, st>>>(
         outlier_idx, n_rows, n_cols, outlier_row_ptr, n_strips, n_chunks, outlier_chunk_ptr);
     return check_cuda(cudaGetLastError(), "chunk_ptr_kernel launch");

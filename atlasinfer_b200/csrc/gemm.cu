@@ -145,7 +145,7 @@ __device__ __forceinline__ void dequant4(uint32_t w, __half2 scale2, uint32_t &l
 struct GemmParams {
     const uint8_t *tiles;
     const uint16_t *scales_t;   // [row/128][block][row%128]
-    const int32_t *chunk_ptr;   // [strip][n_chunks + 1]
+    const int32_t *chunk_ptr;   // [strip][k_tiles + 1]
     const uint32_t *entries;    // row%16 << 24 | column, strip-major, column-sorted
     const uint16_t *ovals;      // values in the order of `entries`
     const uint16_t *bias;
@@ -468,7 +468,7 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
     p.n_cols = (int)n_cols;
     p.bs = block_size;
     p.k_tiles = (int)(n_cols / 64);
-    p.n_chunks = (int)ceil_div_i64(n_cols, 256);
+    p.n_chunks = (int)(n_cols / 64);
     p.out_bf16 = dtype == ATLAS_DTYPE_BF16;
     p.error_flag = status;
     dim3 grid((unsigned)ceil_div_i64(n_rows, GM_BM), (unsigned)ceil_div_i64(m, GM_BN), 1);

@@ -32,6 +32,8 @@
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -52,7 +54,7 @@ struct GemvParams {
     int64_t ldx;
     const uint8_t *tiles;
     const uint16_t *scales_t;   // [row/128][block][row%128]
-    const int32_t *chunk_ptr;   // [strip][n_chunks + 1]
+    const int32_t *chunk_ptr;   // [strip][k_tiles + 1]: first outlier entry with column >= 64 * c
     const uint32_t *entries;    // row%16 << 24 | column, strip-major, column-sorted
     const uint16_t *ovals;      // fp16 outlier values in the order of `entries`
     int n_rows;
@@ -69,6 +71,7 @@ struct GemvParams {
     int splits;         // cluster size S
     int x_vec_ok;       // x rows allow 16-byte loads
     int *status;        // device int, set non-zero if a bounded wait ran out (may be null)
+    int bs_shift;       // log2(block size) when it is a power of two, else -1
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -194,7 +197,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvParams p) {
         }
     }
     // outlier ranges of this warp's strip, per pass, come from chunk_ptr (weights as well)
-    const int32_t *cptr = p.chunk_ptr + (int64_t)(row_strip >> 4) * (p.n_chunks + 1);
+    const int32_t *cptr = p.chunk_ptr + (int64_t)(row_strip >> 4) * (p.k_tiles + 1);
 
     float acc[MT][4];
 #pragma unroll
@@ -282,8 +285,8 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvParams p) {
 
         // ---- sparse part: outliers of this warp's strip inside the pass, 16 per MMA ----------
         {
-            const int e_begin = __ldg(cptr + (pass_begin >> 2));
-            const int e_end = __ldg(cptr + min((pass_end + 3) >> 2, p.n_chunks));
+            const int e_begin = __ldg(cptr + pass_begin);
+            const int e_end = __ldg(cptr + pass_end);
             for (int e0 = e_begin + wk * 16; e0 < e_end; e0 += WK * 16) {
                 uint32_t av[4];   // A fragment: values of slots (2tig,2tig+1) and (2tig+8,2tig+9) for rows g, g+8
                 int cols[4];
@@ -375,7 +378,8 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(GemvParams p) {
 // short: no activation staging, no cluster, one __syncthreads.  A warp loads its codes (16-byte
 // loads, 1 KB per warp and step, contiguous) and scales before the dependency wait, its
 // activations after it (straight from global memory: x is a few KB and stays in L1/L2), and the
-// CTA folds the per-warp partial sums through 8 KB of shared memory.
+// CTA folds the per-warp partial sums through 8 KB of shared memory.  Codes, scales, the first
+// outlier entries and the bias are requested before griddepcontrol.wait.
 constexpr int GS_MAX_WARPS = 16;
 constexpr int GS_UNROLL = 2;
 
@@ -412,40 +416,84 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, 2) gemv_strip_kernel(GemvPa
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int g = lane >> 2, tig = lane & 3;
     const int strip = blockIdx.x;
-    const int c0 = (int)((int64_t)p.n_chunks * warp / nwarps), c1 = (int)((int64_t)p.n_chunks * (warp + 1) / nwarps);
+    const int c0 = (p.n_chunks * warp) / nwarps, c1 = (p.n_chunks * (warp + 1)) / nwarps;
     const int kt0 = c0 * 4, kt1 = min(c1 * 4, p.k_tiles);
 
-    const uint8_t *wbase = p.tiles + (((int64_t)(strip >> 3) * p.k_tiles) * 8 + (strip & 7)) * 1024 + lane * 16;
-    const uint16_t *sbase = p.scales_t + ((int64_t)(strip >> 3) * p.blocks_per_row) * 128 + (strip & 7) * 16 + g;
-    const uint16_t *xrow = reinterpret_cast<const uint16_t *>(p.x) + (int64_t)g * p.ldx + tig * 16;
-    const bool xvalid = g < p.m;
-    const int32_t *cptr = p.chunk_ptr + (int64_t)strip * (p.n_chunks + 1);
+    const uint8_t *wbase = p.tiles + ((size_t)(strip >> 3) * p.k_tiles * 8 + (strip & 7)) * 1024 + lane * 16;
+    const uint16_t *sbase = p.scales_t + (size_t)(strip >> 3) * p.blocks_per_row * 128 + (strip & 7) * 16 + g;
+    // lanes whose batch row does not exist read row 0: their MMA columns are never stored
+    const uint16_t *xg = reinterpret_cast<const uint16_t *>(p.x) + (size_t)(g < p.m ? g : 0) * p.ldx;
+    const uint16_t *xrow = xg + tig * 16;
 
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    bool waited = false;
-    for (int kt = kt0; kt < kt1; kt += GS_UNROLL) {
-        uint4 wa[GS_UNROLL], wb[GS_UNROLL];
-        uint16_t sa[GS_UNROLL], sb[GS_UNROLL];
+    // ---- weights first: none of this depends on earlier kernels of the stream ----------------------
+    uint4 wa[GS_UNROLL], wb[GS_UNROLL];
+    uint16_t sa[GS_UNROLL], sb[GS_UNROLL];
+    auto load_batch = [&](int kt) {
 #pragma unroll
         for (int u = 0; u < GS_UNROLL; ++u) {
             if (kt + u < kt1) {
-                const uint8_t *tp = wbase + (int64_t)(kt + u) * 8192;
+                const uint8_t *tp = wbase + (size_t)(kt + u) * 8192;
                 wa[u] = ldg_stream(tp);
                 wb[u] = ldg_stream(tp + 512);
-                const int kb = ((kt + u) * 64 + tig * 16) / p.bs;
-                sa[u] = __ldg(sbase + (int64_t)kb * 128);
-                sb[u] = __ldg(sbase + (int64_t)kb * 128 + 8);
+                const int kb = p.bs_shift >= 0 ? ((kt + u) * 64 + tig * 16) >> p.bs_shift : ((kt + u) * 64 + tig * 16) / p.bs;
+                sa[u] = __ldg(sbase + (size_t)kb * 128);
+                sb[u] = __ldg(sbase + (size_t)kb * 128 + 8);
             }
         }
-        if (!waited) {  // weights above do not depend on earlier kernels; activations below do
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            waited = true;
+    };
+    load_batch(kt0);
+    // first group of outlier entries of the strip inside this warp's columns, and the bias
+    const int32_t *cptr = p.chunk_ptr + (size_t)strip * (p.k_tiles + 1);
+    int e_begin = 0, e_end = 0;
+    if (kt0 < kt1) { e_begin = __ldg(cptr + kt0); e_end = __ldg(cptr + kt1); }
+    uint32_t pre_ent[4], pre_val[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int e = e_begin + 2 * tig + (q & 1) + (q >> 1) * 8;
+        pre_ent[q] = 0xff000000u;
+        pre_val[q] = 0;
+        if (e < e_end) { pre_ent[q] = __ldg(p.entries + e); pre_val[q] = __ldg(p.ovals + e); }
+    }
+    const int rL = tid >> 2, rj = tid & 3;              // (lane, component) this thread reduces at the end
+    const int out_row = (rL >> 2) + (rj >> 1) * 8, out_m = (rL & 3) * 2 + (rj & 1);
+    const int out_n = strip * 16 + out_row;
+    float bias_v = 0.f;
+    if (tid < 128 && p.bias && out_n < p.n_rows) bias_v = __half2float(__ushort_as_half(__ldg(p.bias + out_n)));
+
+    // ---- activations: only after the earlier kernels of the stream have completed ------------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    auto outlier_mma = [&](const uint32_t (&ent)[4], const uint32_t (&val)[4]) {
+        int rws[4];
+        uint32_t xq[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            rws[q] = (int)(ent[q] >> 24);
+            xq[q] = __ldg(xg + (ent[q] & 0xffffffu));
         }
+        const uint32_t a0 = (rws[0] == g ? val[0] : 0u) | (rws[1] == g ? val[1] : 0u) << 16;
+        const uint32_t a1 = (rws[0] == g + 8 ? val[0] : 0u) | (rws[1] == g + 8 ? val[1] : 0u) << 16;
+        const uint32_t a2 = (rws[2] == g ? val[2] : 0u) | (rws[3] == g ? val[3] : 0u) << 16;
+        const uint32_t a3 = (rws[2] == g + 8 ? val[2] : 0u) | (rws[3] == g + 8 ? val[3] : 0u) << 16;
+        uint32_t b0 = xq[0] | xq[1] << 16, b1 = xq[2] | xq[3] << 16;
+        if (BF16) {
+            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b0) : "f"(__uint_as_float(xq[1] << 16)), "f"(__uint_as_float(xq[0] << 16)));
+            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b1) : "f"(__uint_as_float(xq[3] << 16)), "f"(__uint_as_float(xq[2] << 16)));
+        }
+        mma_f16(acc, a0, a1, a2, a3, b0, b1);
+    };
+    if (e_begin < e_end) outlier_mma(pre_ent, pre_val);   // its activation gathers overlap the K loop's loads
+
+    for (int kt = kt0; kt < kt1; kt += GS_UNROLL) {
+        if (kt != kt0) load_batch(kt);
+        uint32_t xv[GS_UNROLL][8];
+#pragma unroll
+        for (int u = 0; u < GS_UNROLL; ++u)
+            if (kt + u < kt1) load_x16<BF16>(xrow + (kt + u) * 64, true, xv[u]);
 #pragma unroll
         for (int u = 0; u < GS_UNROLL; ++u) {
             if (kt + u < kt1) {
-                uint32_t xv[8];
-                load_x16<BF16>(xrow + (kt + u) * 64, xvalid, xv);
                 const __half2 sa2 = __half2half2(__ushort_as_half(sa[u])), sb2 = __half2half2(__ushort_as_half(sb[u]));
                 const uint32_t wav[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w};
                 const uint32_t wbv[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
@@ -454,60 +502,31 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, 2) gemv_strip_kernel(GemvPa
                     uint32_t alo, ahi, blo, bhi;
                     dequant4(wav[i], sa2, alo, ahi);
                     dequant4(wbv[i], sb2, blo, bhi);
-                    mma_f16(acc, alo, blo, ahi, bhi, xv[2 * i], xv[2 * i + 1]);
+                    mma_f16(acc, alo, blo, ahi, bhi, xv[u][2 * i], xv[u][2 * i + 1]);
                 }
             }
         }
     }
-    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    // outliers of the strip inside this warp's chunks, 16 per MMA
-    if (kt0 < kt1) {
-        const int e_begin = __ldg(cptr + c0), e_end = __ldg(cptr + c1);
-        const uint16_t *xg = reinterpret_cast<const uint16_t *>(p.x) + (int64_t)g * p.ldx;
-        for (int e0 = e_begin; e0 < e_end; e0 += 16) {
-            int cols[4], rws[4];
-            uint32_t vals[4];
+    for (int e0 = e_begin + 16; e0 < e_end; e0 += 16) {    // remaining outlier groups, 16 per MMA
+        uint32_t ent[4], val[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int e = e0 + 2 * tig + (q & 1) + (q >> 1) * 8;
-                uint32_t ent = 0xff000000u;
-                uint32_t v = 0;
-                if (e < e_end) { ent = __ldg(p.entries + e); v = __ldg(p.ovals + e); }
-                cols[q] = (int)(ent & 0xffffffu);
-                rws[q] = (int)(ent >> 24);
-                vals[q] = v;
-            }
-            const uint32_t a0 = (rws[0] == g ? vals[0] : 0u) | (rws[1] == g ? vals[1] : 0u) << 16;
-            const uint32_t a1 = (rws[0] == g + 8 ? vals[0] : 0u) | (rws[1] == g + 8 ? vals[1] : 0u) << 16;
-            const uint32_t a2 = (rws[2] == g ? vals[2] : 0u) | (rws[3] == g ? vals[3] : 0u) << 16;
-            const uint32_t a3 = (rws[2] == g + 8 ? vals[2] : 0u) | (rws[3] == g + 8 ? vals[3] : 0u) << 16;
-            uint32_t xq[4] = {0, 0, 0, 0};
-            if (xvalid) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) xq[q] = __ldg(xg + cols[q]);
-            }
-            uint32_t b0 = xq[0] | xq[1] << 16, b1 = xq[2] | xq[3] << 16;
-            if (BF16) {
-                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b0) : "f"(__uint_as_float(xq[1] << 16)), "f"(__uint_as_float(xq[0] << 16)));
-                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b1) : "f"(__uint_as_float(xq[3] << 16)), "f"(__uint_as_float(xq[2] << 16)));
-            }
-            mma_f16(acc, a0, a1, a2, a3, b0, b1);
+        for (int q = 0; q < 4; ++q) {
+            const int e = e0 + 2 * tig + (q & 1) + (q >> 1) * 8;
+            ent[q] = 0xff000000u;
+            val[q] = 0;
+            if (e < e_end) { ent[q] = __ldg(p.entries + e); val[q] = __ldg(p.ovals + e); }
         }
+        outlier_mma(ent, val);
     }
 
     part[warp][lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     __syncthreads();
     if (tid < 128) {
-        const int L = tid >> 2, j = tid & 3;       // lane and accumulator index being reduced
-        float s = 0.f;
-        for (int w = 0; w < nwarps; ++w) s += reinterpret_cast<const float *>(&part[w][L])[j];
-        const int row = (L >> 2) + (j >> 1) * 8, m = (L & 3) * 2 + (j & 1);
-        const int n = strip * 16 + row;
-        if (m < p.m && n < p.n_rows) {
-            if (p.bias) s += __half2float(__ushort_as_half(__ldg(p.bias + n)));
-            if (BF16) reinterpret_cast<__nv_bfloat16 *>(p.y)[(int64_t)m * p.ldy + n] = __float2bfloat16_rn(s);
-            else reinterpret_cast<__half *>(p.y)[(int64_t)m * p.ldy + n] = __float2half_rn(s);
+        float s = bias_v;
+        for (int w = 0; w < nwarps; ++w) s += reinterpret_cast<const float *>(&part[w][rL])[rj];
+        if (out_m < p.m && out_n < p.n_rows) {
+            if (BF16) reinterpret_cast<__nv_bfloat16 *>(p.y)[(size_t)out_m * p.ldy + out_n] = __float2bfloat16_rn(s);
+            else reinterpret_cast<__half *>(p.y)[(size_t)out_m * p.ldy + out_n] = __float2half_rn(s);
         }
     }
 }
@@ -662,6 +681,7 @@ extern "C" int atlas_qlinear_gemv(const void *x, int dtype, int64_t m, int64_t l
         p.splits = splits;
         p.x_vec_ok = (((uintptr_t)x & 15) == 0) && (ldx % 8 == 0);
         p.status = status;
+        p.bs_shift = (block_size & (block_size - 1)) == 0 ? __builtin_ctz((unsigned)block_size) : -1;
 
         if (mt == 1 && p.x_vec_ok) {
             rc = launch_gemv_strip(p, st);

@@ -34,7 +34,7 @@ class KernelLayout(NamedTuple):
     tiles: torch.Tensor            # uint8, tile-major dense codes + 128
     scales_tiled: torch.Tensor     # fp16, [N/128][K/block][128]
     row_ptr: torch.Tensor          # int32 [N + 1], CSR over the canonical outlier streams
-    chunk_ptr: torch.Tensor        # int32 [N_padded/16][ceil(K/256) + 1]
+    chunk_ptr: torch.Tensor        # int32 [N_padded/16][K/64 + 1]
     entries: torch.Tensor          # int32 (row%16 << 24 | col), strip-major, column-sorted
     vals_sorted: torch.Tensor      # fp16 outlier values in the order of `entries`
     n_rows: int
@@ -89,7 +89,7 @@ def build_kernel_layout(q: QuantizedTensor) -> KernelLayout:
         tiles = torch.empty(int(L.atlas_tiles_bytes(n, k)), dtype=torch.uint8, device=dev)
         scales_tiled = torch.empty(n_pad * (k // bs), dtype=torch.float16, device=dev)
         row_ptr = torch.empty(n + 1, dtype=torch.int32, device=dev)
-        chunk_ptr = torch.empty((n_pad // 16) * ((k + 255) // 256 + 1), dtype=torch.int32, device=dev)
+        chunk_ptr = torch.empty((n_pad // 16) * (k // 64 + 1), dtype=torch.int32, device=dev)
         entries = torch.empty(n_out, dtype=torch.int32, device=dev)
         vals_sorted = torch.empty(n_out, dtype=torch.float16, device=dev)
         codes, oidx = q.fp8_data.contiguous(), q.outlier_indices.contiguous()

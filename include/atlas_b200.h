@@ -130,8 +130,8 @@ ATLAS_API int atlas_dequantize(const int8_t *codes, int64_t n_codes, const void 
  *                    [row/128][block][row%128] (0 for padding rows)
  *   outlier_row_ptr  n_rows + 1 int32: CSR row starts into the canonical
  *                    outlier streams
- *   outlier_chunk_ptr  (rows_padded/16) x (ceil(n_cols/256) + 1) int32: for
- *                    each 16-row strip, the first entry with column >= 256*c
+ *   outlier_chunk_ptr  (rows_padded/16) x (n_cols/64 + 1) int32: for each
+ *                    16-row strip, the first entry with column >= 64*c
  *   outlier_entries  n_outliers uint32, (row%16) << 24 | column, grouped by
  *                    strip and sorted by column within a strip
  *   outlier_vals_sorted  n_outliers fp16 in the order of outlier_entries
@@ -160,8 +160,8 @@ ATLAS_API int atlas_repack(const int8_t *codes, int64_t n_codes, const void *out
  *
  * atlas_qlinear_gemv: decode shapes, any m >= 1 (rows are processed in groups
  * of up to 32; intended for m <= 32).  HBM-bound: streams the tiles once per
- * group through per-warp bulk-copy rings, dequantises in registers and adds
- * the outlier products in the same launch.  Launched with programmatic
+ * group through per-warp shared-memory rings, dequantises in registers and
+ * adds the outlier products in the same launch.  Launched with programmatic
  * dependent launch: only weights are read before the stream's earlier work
  * has completed.
  *
