@@ -9,10 +9,11 @@
 //
 // One CTA computes a 128 (output features) x 256 (tokens) tile:
 //   warp 0      producer: per 64-wide K step a 1-D bulk copy of the 8 KB code
-//               tile (the tile-major layout makes it contiguous) and a 2-D TMA
+//               tile (the tile-major layout makes it contiguous), one of the 256 B
+//               of scales of the step's block, and a 2-D TMA
 //               load of the 256 x 64 fp16 activation tile (128-byte swizzle),
 //               both completing on the stage's `full` mbarrier
-//   warps 2-5   dequantizers: codes -> fp16 A-operand tile in the canonical
+//   warps 2-9   dequantizers (one 16-row strip each): codes -> fp16 A-operand tile in the canonical
 //               K-major 128-byte-swizzled layout, outliers of the tile written
 //               over their (zero-coded) slots from the strip-sorted side-table, then
 //               fence.proxy.async + arrive on `a_ready`
@@ -20,8 +21,8 @@
 //               fp32 accumulate in TMEM) four times per stage and commits the
 //               stage's `empty` mbarrier; after the last step it commits
 //               `acc_full`
-//   warps 2-5   epilogue: tcgen05.ld of their TMEM lane quarter, + bias,
-//               convert, store y
+//   warps 2-9   epilogue: tcgen05.ld of their TMEM lane quarter (two warps per quarter,
+//               half of the columns each), + bias, convert, store y
 // Every mbarrier wait is bounded; if one runs out the CTA sets the caller's status word,
 // skips the rest of its work, frees its TMEM and returns.
 //
@@ -35,7 +36,8 @@
 namespace atlas {
 namespace {
 
-constexpr int GM_THREADS = 192;
+constexpr int GM_DQ_WARPS = 8;                       // dequantizer / epilogue warps (one 16-row strip each)
+constexpr int GM_THREADS = 64 + GM_DQ_WARPS * 32;   // + producer warp + MMA warp
 constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
 constexpr int GM_BN = 256;  // tokens per CTA = UMMA N
 constexpr int GM_BK = 64;   // K per pipeline stage (one 128-byte swizzle row of fp16)
@@ -44,7 +46,8 @@ constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2;  // 16 KB fp16 weight tile
 constexpr uint32_t B_BYTES = GM_BN * GM_BK * 2;  // 32 KB fp16 activation tile
 constexpr uint32_t C_BYTES = GM_BM * GM_BK;      // 8 KB code tile
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + C_BYTES;
-constexpr uint32_t GM_SMEM = GM_STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t S_BYTES = 256;                    // one scale block: 128 rows x fp16
+constexpr uint32_t GM_SMEM = GM_STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + GM_STAGES * S_BYTES;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr int GM_SPIN_LIMIT = 1 << 20;
 
@@ -157,6 +160,7 @@ struct GemmParams {
     int bs;
     int k_tiles;
     int n_chunks;
+    int bs_tiles;   // k-tiles per scale block when block_size % 64 == 0 (scales staged by the producer), else 0
     int out_bf16;
     int *error_flag;
 };
@@ -174,6 +178,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     const uint32_t accfull_bar = bars + 8u * (3 * GM_STAGES);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + GM_STAGES * STAGE_BYTES + 8 * (3 * GM_STAGES + 1));
     volatile int *s_abort = reinterpret_cast<volatile int *>(base_ptr + GM_STAGES * STAGE_BYTES + 8 * (3 * GM_STAGES + 1) + 8);
+    const uint32_t sc_stage = base + GM_STAGES * STAGE_BYTES + 256;  // [stage][128] fp16 scales of the stage's block
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * GM_BM;  // first weight row (output feature) of the tile
@@ -183,7 +188,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     if (tid == 0) {
         for (int s = 0; s < GM_STAGES; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(aready_bar(s), 128);
+            mbar_init(aready_bar(s), GM_DQ_WARPS * 32);
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(accfull_bar, 1);
@@ -209,9 +214,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
                 if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1)) { *s_abort = 1; break; }
                 if (*s_abort) break;
                 const uint32_t st = base + s * STAGE_BYTES;
-                mbar_arrive_expect_tx(full_bar(s), B_BYTES + C_BYTES);
+                mbar_arrive_expect_tx(full_bar(s), B_BYTES + C_BYTES + (p.bs_tiles ? S_BYTES : 0));
                 tma_load_2d(st + A_BYTES, &x_map, it * GM_BK, m0, full_bar(s));
                 bulk_load_1d(st + A_BYTES + B_BYTES, ctile + (size_t)it * C_BYTES, C_BYTES, full_bar(s));
+                if (p.bs_tiles)
+                    bulk_load_1d(sc_stage + s * S_BYTES,
+                                 p.scales_t + ((size_t)blockIdx.x * (p.n_cols / p.bs) + it / p.bs_tiles) * 128, S_BYTES, full_bar(s));
             }
         }
     } else if (warp == 1) {
@@ -235,61 +243,63 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         }
     } else {
         // ------------------------------ dequantizers, then epilogue ------------------------------
-        const int dw = warp - 2;               // 0..3: strips 2*dw and 2*dw + 1 of the 128-row tile
+        const int dw = warp - 2;               // 0..7: strip dw of the 128-row tile
         const int g = lane >> 2, tig = lane & 3;
         const int bpr = p.n_cols / p.bs;
         const uint16_t *sc_tile = p.scales_t + (int64_t)blockIdx.x * bpr * 128;
-        // rows of the tile this thread rebuilds in every K step: 2 strips x (g, g + 8)
-        int rows[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) rows[i] = (2 * dw + (i >> 1)) * 16 + (i & 1) * 8 + g;
-        // outlier cursors of the two strips (lists are sorted by column)
-        int cur[2], end[2];
-        uint32_t nent[2];
-#pragma unroll
-        for (int si = 0; si < 2; ++si) {
-            const int64_t strip = (int64_t)blockIdx.x * 8 + 2 * dw + si;
-            cur[si] = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1));
-            end[si] = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + p.n_chunks);
-            nent[si] = cur[si] < end[si] ? __ldg(p.entries + cur[si]) : 0x00ffffffu;
-        }
+        const int r0 = dw * 16 + g, r1 = r0 + 8;   // the two rows of the tile this thread rebuilds in every K step
+        // outlier cursor of the strip (its list is sorted by column)
+        const int64_t strip = (int64_t)blockIdx.x * 8 + dw;
+        int cur = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1));
+        const int end = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + p.n_chunks);
+        uint32_t nent = cur < end ? __ldg(p.entries + cur) : 0x00ffffffu;
+        const uint32_t sw0 = (uint32_t)((2 * tig) ^ g) << 4, sw1 = (uint32_t)((2 * tig + 1) ^ g) << 4;  // swizzled 16-byte chunks
         bool ok = true;
         for (int it = 0; it < KT && ok; ++it) {
             const int s = it % GM_STAGES, round = it / GM_STAGES;
             if (!mbar_wait(full_bar(s), round & 1) || *s_abort) { ok = false; break; }
             unsigned char *stp = base_ptr + s * STAGE_BYTES;
-            const unsigned char *codes = stp + A_BYTES + B_BYTES;
+            const unsigned char *codes = stp + A_BYTES + B_BYTES + (dw * 2 * 32 + lane) * 16;
             const int k0 = it * GM_BK;
-            const int kb = (k0 + tig * 16) / p.bs;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = rows[i];
-                const uint4 c = *reinterpret_cast<const uint4 *>(codes + (((2 * dw + (i >> 1)) * 2 + (i & 1)) * 32 + lane) * 16);
-                const __half2 sc2 = __half2half2(__ushort_as_half(__ldg(sc_tile + (int64_t)kb * 128 + r)));
-                uint4 o0, o1;
-                dequant4(c.x, sc2, o0.x, o0.y);
-                dequant4(c.y, sc2, o0.z, o0.w);
-                dequant4(c.z, sc2, o1.x, o1.y);
-                dequant4(c.w, sc2, o1.z, o1.w);
-                unsigned char *rowp = stp + (r >> 3) * 1024 + (r & 7) * 128;
-                *reinterpret_cast<uint4 *>(rowp + (((2 * tig) ^ (r & 7)) << 4)) = o0;      // k 16*tig .. +7
-                *reinterpret_cast<uint4 *>(rowp + (((2 * tig + 1) ^ (r & 7)) << 4)) = o1;  // k 16*tig+8 .. +15
+            const uint4 c0 = *reinterpret_cast<const uint4 *>(codes);          // row r0, k 16*tig .. +15
+            const uint4 c1 = *reinterpret_cast<const uint4 *>(codes + 512);    // row r1
+            __half sh0, sh1;
+            if (p.bs_tiles) {
+                const uint16_t *scs = reinterpret_cast<const uint16_t *>(base_ptr + GM_STAGES * STAGE_BYTES + 256 + s * S_BYTES);
+                sh0 = __ushort_as_half(scs[r0]);
+                sh1 = __ushort_as_half(scs[r1]);
+            } else {
+                const int kb = (k0 + tig * 16) / p.bs;
+                sh0 = __ushort_as_half(__ldg(sc_tile + (int64_t)kb * 128 + r0));
+                sh1 = __ushort_as_half(__ldg(sc_tile + (int64_t)kb * 128 + r1));
             }
-            // outliers of the two strips inside this K step: the lane that rebuilt the 16-column
-            // segment writes the raw fp16 value over the zero-coded slot (same thread: program order)
-#pragma unroll
-            for (int si = 0; si < 2; ++si) {
-                while ((int)(nent[si] & 0xffffffu) < k0 + GM_BK) {
-                    const int kk = (int)(nent[si] & 0xffffffu) - k0;
-                    const int rs = (int)(nent[si] >> 24);
-                    if ((rs & 7) == g && (kk >> 4) == tig) {
-                        const int r = (2 * dw + si) * 16 + rs;
-                        unsigned char *rowp = stp + (r >> 3) * 1024 + (r & 7) * 128;
-                        *reinterpret_cast<uint16_t *>(rowp + (((kk >> 3) ^ (r & 7)) << 4) + (kk & 7) * 2) = __ldg(p.ovals + cur[si]);
-                    }
-                    ++cur[si];
-                    nent[si] = cur[si] < end[si] ? __ldg(p.entries + cur[si]) : 0x00ffffffu;
+            const __half2 s02 = __half2half2(sh0), s12 = __half2half2(sh1);
+            uint4 o0, o1, o2, o3;
+            dequant4(c0.x, s02, o0.x, o0.y);
+            dequant4(c0.y, s02, o0.z, o0.w);
+            dequant4(c0.z, s02, o1.x, o1.y);
+            dequant4(c0.w, s02, o1.z, o1.w);
+            dequant4(c1.x, s12, o2.x, o2.y);
+            dequant4(c1.y, s12, o2.z, o2.w);
+            dequant4(c1.z, s12, o3.x, o3.y);
+            dequant4(c1.w, s12, o3.z, o3.w);
+            unsigned char *row0 = stp + (r0 >> 3) * 1024 + g * 128;   // r0 & 7 == r1 & 7 == g
+            unsigned char *row1 = row0 + 1024;
+            *reinterpret_cast<uint4 *>(row0 + sw0) = o0;   // k 16*tig .. +7
+            *reinterpret_cast<uint4 *>(row0 + sw1) = o1;   // k 16*tig+8 .. +15
+            *reinterpret_cast<uint4 *>(row1 + sw0) = o2;
+            *reinterpret_cast<uint4 *>(row1 + sw1) = o3;
+            // outliers of the strip inside this K step: the lane that rebuilt the 16-column segment
+            // writes the raw fp16 value over the zero-coded slot (same thread: program order)
+            while ((int)(nent & 0xffffffu) < k0 + GM_BK) {
+                const int kk = (int)(nent & 0xffffffu) - k0;
+                const int rs = (int)(nent >> 24);
+                if ((rs & 7) == g && (kk >> 4) == tig) {
+                    unsigned char *rowp = stp + (dw * 2 + (rs >> 3)) * 1024 + g * 128;
+                    *reinterpret_cast<uint16_t *>(rowp + (((kk >> 3) ^ g) << 4) + (kk & 7) * 2) = __ldg(p.ovals + cur);
                 }
+                ++cur;
+                nent = cur < end ? __ldg(p.entries + cur) : 0x00ffffffu;
             }
             fence_async_smem();  // make the generic-proxy writes visible to the tensor core's reads
             mbar_arrive(aready_bar(s));
@@ -299,10 +309,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         // epilogue: TMEM lane = output feature, column = token
         if (mbar_wait(accfull_bar, 0) && !*s_abort) {
             tcgen05_fence_after();
-            const int q = warp & 3;  // the TMEM lane quarter this warp may read
+            const int q = warp & 3;              // the TMEM lane quarter this warp may read
+            const int half = (warp - 2) >> 2;    // two warps share a quarter: columns [0,128) and [128,256)
             const int n = n0 + q * 32 + lane;
             const float bv = (p.bias && n < p.n_rows) ? __half2float(__ushort_as_half(__ldg(p.bias + n))) : 0.f;
-            for (int c = 0; c < GM_BN / 32; ++c) {
+            for (int c = half * (GM_BN / 64); c < (half + 1) * (GM_BN / 64); ++c) {
                 if (m0 + c * 32 >= p.m) break;  // warp-uniform: no tokens left in this tile
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
@@ -469,6 +480,7 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
     p.bs = block_size;
     p.k_tiles = (int)(n_cols / 64);
     p.n_chunks = (int)(n_cols / 64);
+    p.bs_tiles = block_size % 64 == 0 ? block_size / 64 : 0;
     p.out_bf16 = dtype == ATLAS_DTYPE_BF16;
     p.error_flag = status;
     dim3 grid((unsigned)ceil_div_i64(n_rows, GM_BM), (unsigned)ceil_div_i64(m, GM_BN), 1);
