@@ -7,22 +7,22 @@
 // tile by tile in shared memory and consumed at once by the 5th-generation
 // tensor cores, so it never exists in global memory.
 //
-// One CTA computes a 128 (output features) x 256 (tokens) tile:
-//   warp 0      producer: per 64-wide K step a 1-D bulk copy of the 8 KB code
-//               tile (the tile-major layout makes it contiguous), one of the 256 B
-//               of scales of the step's block, and a 2-D TMA
-//               load of the 256 x 64 fp16 activation tile (128-byte swizzle),
-//               both completing on the stage's `full` mbarrier
-//   warps 2-9   dequantizers (one 16-row strip each): codes -> fp16 A-operand tile in the canonical
-//               K-major 128-byte-swizzled layout, outliers of the tile written
-//               over their (zero-coded) slots from the strip-sorted side-table, then
-//               fence.proxy.async + arrive on `a_ready`
-//   warp 1      one thread issues tcgen05.mma (M=128, N=256, K=16, fp16 in,
-//               fp32 accumulate in TMEM) four times per stage and commits the
-//               stage's `empty` mbarrier; after the last step it commits
-//               `acc_full`
-//   warps 2-9   epilogue: tcgen05.ld of their TMEM lane quarter (two warps per quarter,
-//               half of the columns each), + bias, convert, store y
+// One CTA computes a 128 (output features) x 256 (tokens) tile with three rings in shared memory:
+// codes (8 slots of 8 KB: they come from HBM and need the deepest prefetch), activations (3 slots
+// of 32 KB, L2-resident) and rebuilt fp16 weights (3 slots of 16 KB, same index as the activations).
+//   warp 0      activation producer: per 64-wide K step a 2-D TMA load of the 256 x 64 fp16
+//               activation tile (128-byte swizzle) completing on `full_x`
+//   warp 2      code producer: a 1-D bulk copy of the step's 8 KB code tile (contiguous in the
+//               tile-major layout) and of the 256 B of scales of its block, completing on `full_c`
+//   warps 3-10  dequantizers (one 16-row strip each): codes -> fp16 A-operand tile in the canonical
+//               K-major 128-byte-swizzled layout, outliers of the tile written over their
+//               (zero-coded) slots from the strip-sorted side-table, then fence.proxy.async +
+//               arrive on `a_ready`; the code slot is released on `empty_c`
+//   warp 1      one thread issues tcgen05.mma (M=128, N=256, K=16, fp16 in, fp32 accumulate in
+//               TMEM) four times per step and commits the slot's `mma_done` mbarrier (which frees
+//               both the activation and the weight slot); after the last step it commits `acc_full`
+//   warps 3-10  epilogue: tcgen05.ld of their TMEM lane quarter (two warps per quarter, half of
+//               the columns each), + bias, convert, store y
 // Every mbarrier wait is bounded; if one runs out the CTA sets the caller's status word,
 // skips the rest of its work, frees its TMEM and returns.
 //
@@ -37,17 +37,20 @@ namespace atlas {
 namespace {
 
 constexpr int GM_DQ_WARPS = 8;                       // dequantizer / epilogue warps (one 16-row strip each)
-constexpr int GM_THREADS = 64 + GM_DQ_WARPS * 32;   // + producer warp + MMA warp
+constexpr int GM_CTRL_WARPS = 3;                     // activation producer, MMA issuer, code producer
+constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_WARPS) * 32;
 constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
 constexpr int GM_BN = 256;  // tokens per CTA = UMMA N
-constexpr int GM_BK = 64;   // K per pipeline stage (one 128-byte swizzle row of fp16)
-constexpr int GM_STAGES = 4;
+constexpr int GM_BK = 64;   // K per pipeline step (one 128-byte swizzle row of fp16)
+constexpr int GM_XS = 3;    // activation / weight-tile ring depth
+constexpr int GM_CS = 8;    // code ring depth
 constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2;  // 16 KB fp16 weight tile
 constexpr uint32_t B_BYTES = GM_BN * GM_BK * 2;  // 32 KB fp16 activation tile
 constexpr uint32_t C_BYTES = GM_BM * GM_BK;      // 8 KB code tile
-constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + C_BYTES;
-constexpr uint32_t S_BYTES = 256;                    // one scale block: 128 rows x fp16
-constexpr uint32_t GM_SMEM = GM_STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + GM_STAGES * S_BYTES;
+constexpr uint32_t S_BYTES = 256;                // one scale block: 128 rows x fp16
+constexpr uint32_t OFF_A = 0, OFF_B = GM_XS * A_BYTES, OFF_C = OFF_B + GM_XS * B_BYTES, OFF_BAR = OFF_C + GM_CS * C_BYTES;
+constexpr uint32_t OFF_S = OFF_BAR + 256;
+constexpr uint32_t GM_SMEM = OFF_S + GM_CS * S_BYTES + 1024 /*alignment slack*/;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr int GM_SPIN_LIMIT = 1 << 20;
 
@@ -171,14 +174,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;          // operand tiles need 1024-byte alignment
     unsigned char *base_ptr = smem_raw + (base - raw);
-    const uint32_t bars = base + GM_STAGES * STAGE_BYTES;   // mbarriers, 8 bytes each
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto aready_bar = [&](int s) { return bars + 8u * (GM_STAGES + s); };
-    auto empty_bar = [&](int s) { return bars + 8u * (2 * GM_STAGES + s); };
-    const uint32_t accfull_bar = bars + 8u * (3 * GM_STAGES);
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + GM_STAGES * STAGE_BYTES + 8 * (3 * GM_STAGES + 1));
-    volatile int *s_abort = reinterpret_cast<volatile int *>(base_ptr + GM_STAGES * STAGE_BYTES + 8 * (3 * GM_STAGES + 1) + 8);
-    const uint32_t sc_stage = base + GM_STAGES * STAGE_BYTES + 256;  // [stage][128] fp16 scales of the stage's block
+    const uint32_t bars = base + OFF_BAR;   // mbarriers, 8 bytes each
+    auto full_x = [&](int s) { return bars + 8u * s; };
+    auto aready_bar = [&](int s) { return bars + 8u * (GM_XS + s); };
+    auto mma_done = [&](int s) { return bars + 8u * (2 * GM_XS + s); };
+    auto full_c = [&](int s) { return bars + 8u * (3 * GM_XS + s); };
+    auto empty_c = [&](int s) { return bars + 8u * (3 * GM_XS + GM_CS + s); };
+    const uint32_t accfull_bar = bars + 8u * (3 * GM_XS + 2 * GM_CS);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + OFF_BAR + 8 * (3 * GM_XS + 2 * GM_CS + 1));
+    volatile int *s_abort = reinterpret_cast<volatile int *>(base_ptr + OFF_BAR + 8 * (3 * GM_XS + 2 * GM_CS + 1) + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * GM_BM;  // first weight row (output feature) of the tile
@@ -186,10 +190,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     const int KT = p.k_tiles;
 
     if (tid == 0) {
-        for (int s = 0; s < GM_STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
+        for (int s = 0; s < GM_XS; ++s) {
+            mbar_init(full_x(s), 1);
             mbar_init(aready_bar(s), GM_DQ_WARPS * 32);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(mma_done(s), 1);
+        }
+        for (int s = 0; s < GM_CS; ++s) {
+            mbar_init(full_c(s), 1);
+            mbar_init(empty_c(s), GM_DQ_WARPS);
         }
         mbar_init(accfull_bar, 1);
         *s_abort = 0;
@@ -206,20 +214,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ------------------------------ producer ------------------------------
+        // ------------------------------ activation producer ------------------------------
+        if (lane == 0) {
+            for (int it = 0; it < KT; ++it) {
+                const int s = it % GM_XS, round = it / GM_XS;
+                if (round > 0 && !mbar_wait(mma_done(s), (round - 1) & 1)) { *s_abort = 1; break; }
+                if (*s_abort) break;
+                mbar_arrive_expect_tx(full_x(s), B_BYTES);
+                tma_load_2d(base + OFF_B + s * B_BYTES, &x_map, it * GM_BK, m0, full_x(s));
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------ code producer ------------------------------
         if (lane == 0) {
             const uint8_t *ctile = p.tiles + (size_t)blockIdx.x * KT * C_BYTES;
+            const int bpr = p.n_cols / p.bs;
             for (int it = 0; it < KT; ++it) {
-                const int s = it % GM_STAGES, round = it / GM_STAGES;
-                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1)) { *s_abort = 1; break; }
+                const int s = it % GM_CS, round = it / GM_CS;
+                if (round > 0 && !mbar_wait(empty_c(s), (round - 1) & 1)) { *s_abort = 1; break; }
                 if (*s_abort) break;
-                const uint32_t st = base + s * STAGE_BYTES;
-                mbar_arrive_expect_tx(full_bar(s), B_BYTES + C_BYTES + (p.bs_tiles ? S_BYTES : 0));
-                tma_load_2d(st + A_BYTES, &x_map, it * GM_BK, m0, full_bar(s));
-                bulk_load_1d(st + A_BYTES + B_BYTES, ctile + (size_t)it * C_BYTES, C_BYTES, full_bar(s));
+                mbar_arrive_expect_tx(full_c(s), C_BYTES + (p.bs_tiles ? S_BYTES : 0));
+                bulk_load_1d(base + OFF_C + s * C_BYTES, ctile + (size_t)it * C_BYTES, C_BYTES, full_c(s));
                 if (p.bs_tiles)
-                    bulk_load_1d(sc_stage + s * S_BYTES,
-                                 p.scales_t + ((size_t)blockIdx.x * (p.n_cols / p.bs) + it / p.bs_tiles) * 128, S_BYTES, full_bar(s));
+                    bulk_load_1d(base + OFF_S + s * S_BYTES,
+                                 p.scales_t + ((size_t)blockIdx.x * bpr + it / p.bs_tiles) * 128, S_BYTES, full_c(s));
             }
         }
     } else if (warp == 1) {
@@ -227,23 +245,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         if (lane == 0) {
             bool ok = true;
             for (int it = 0; it < KT && ok; ++it) {
-                const int s = it % GM_STAGES, round = it / GM_STAGES;
-                ok = mbar_wait(aready_bar(s), round & 1) && mbar_wait(full_bar(s), round & 1) && !*s_abort;
+                const int s = it % GM_XS, round = it / GM_XS;
+                ok = mbar_wait(aready_bar(s), round & 1) && mbar_wait(full_x(s), round & 1) && !*s_abort;
                 if (!ok) break;
                 tcgen05_fence_after();
-                const uint32_t st = base + s * STAGE_BYTES;
-                const uint64_t da = make_smem_desc(st), db = make_smem_desc(st + A_BYTES);
+                const uint64_t da = make_smem_desc(base + OFF_A + s * A_BYTES), db = make_smem_desc(base + OFF_B + s * B_BYTES);
 #pragma unroll
                 for (int k = 0; k < GM_BK / 16; ++k)  // 32 bytes (16 fp16) further along K per step
                     umma_f16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), GM_IDESC, (it | k) != 0);
-                umma_commit(empty_bar(s));  // arrives when these MMAs have finished reading the stage
+                umma_commit(mma_done(s));  // arrives when these MMAs have finished reading both slots
             }
             if (!ok) *s_abort = 1;
             umma_commit(accfull_bar);  // arrives when every MMA issued so far is complete
         }
     } else {
         // ------------------------------ dequantizers, then epilogue ------------------------------
-        const int dw = warp - 2;               // 0..7: strip dw of the 128-row tile
+        const int dw = warp - GM_CTRL_WARPS;   // 0..7: strip dw of the 128-row tile
         const int g = lane >> 2, tig = lane & 3;
         const int bpr = p.n_cols / p.bs;
         const uint16_t *sc_tile = p.scales_t + (int64_t)blockIdx.x * bpr * 128;
@@ -252,20 +269,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         const int64_t strip = (int64_t)blockIdx.x * 8 + dw;
         int cur = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1));
         const int end = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + p.n_chunks);
-        uint32_t nent = cur < end ? __ldg(p.entries + cur) : 0x00ffffffu;
+        // the warp keeps the next 32 entries of the list in registers, one per lane
+        uint32_t buf_ent = cur + lane < end ? __ldg(p.entries + cur + lane) : 0x00ffffffu;
+        uint32_t buf_val = cur + lane < end ? (uint32_t)__ldg(p.ovals + cur + lane) : 0u;
         const uint32_t sw0 = (uint32_t)((2 * tig) ^ g) << 4, sw1 = (uint32_t)((2 * tig + 1) ^ g) << 4;  // swizzled 16-byte chunks
         bool ok = true;
         for (int it = 0; it < KT && ok; ++it) {
-            const int s = it % GM_STAGES, round = it / GM_STAGES;
-            if (!mbar_wait(full_bar(s), round & 1) || *s_abort) { ok = false; break; }
-            unsigned char *stp = base_ptr + s * STAGE_BYTES;
-            const unsigned char *codes = stp + A_BYTES + B_BYTES + (dw * 2 * 32 + lane) * 16;
+            const int sc_ = it % GM_CS, cround = it / GM_CS;   // code slot
+            const int sa = it % GM_XS, around = it / GM_XS;    // weight-tile slot
+            if (!mbar_wait(full_c(sc_), cround & 1) || *s_abort) { ok = false; break; }
+            const unsigned char *codes = base_ptr + OFF_C + sc_ * C_BYTES + (dw * 2 * 32 + lane) * 16;
             const int k0 = it * GM_BK;
             const uint4 c0 = *reinterpret_cast<const uint4 *>(codes);          // row r0, k 16*tig .. +15
             const uint4 c1 = *reinterpret_cast<const uint4 *>(codes + 512);    // row r1
             __half sh0, sh1;
             if (p.bs_tiles) {
-                const uint16_t *scs = reinterpret_cast<const uint16_t *>(base_ptr + GM_STAGES * STAGE_BYTES + 256 + s * S_BYTES);
+                const uint16_t *scs = reinterpret_cast<const uint16_t *>(base_ptr + OFF_S + sc_ * S_BYTES);
                 sh0 = __ushort_as_half(scs[r0]);
                 sh1 = __ushort_as_half(scs[r1]);
             } else {
@@ -283,26 +302,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
             dequant4(c1.y, s12, o2.z, o2.w);
             dequant4(c1.z, s12, o3.x, o3.y);
             dequant4(c1.w, s12, o3.z, o3.w);
+            // the code slot is in registers: hand it back (one arrival per warp)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_c(sc_));
+            // the weight-tile slot must have been read by the MMAs of its previous use
+            if (around > 0 && !mbar_wait(mma_done(sa), (around - 1) & 1)) { ok = false; break; }
+            unsigned char *stp = base_ptr + OFF_A + sa * A_BYTES;
             unsigned char *row0 = stp + (r0 >> 3) * 1024 + g * 128;   // r0 & 7 == r1 & 7 == g
             unsigned char *row1 = row0 + 1024;
             *reinterpret_cast<uint4 *>(row0 + sw0) = o0;   // k 16*tig .. +7
             *reinterpret_cast<uint4 *>(row0 + sw1) = o1;   // k 16*tig+8 .. +15
             *reinterpret_cast<uint4 *>(row1 + sw0) = o2;
             *reinterpret_cast<uint4 *>(row1 + sw1) = o3;
-            // outliers of the strip inside this K step: the lane that rebuilt the 16-column segment
-            // writes the raw fp16 value over the zero-coded slot (same thread: program order)
-            while ((int)(nent & 0xffffffu) < k0 + GM_BK) {
-                const int kk = (int)(nent & 0xffffffu) - k0;
-                const int rs = (int)(nent >> 24);
-                if ((rs & 7) == g && (kk >> 4) == tig) {
-                    unsigned char *rowp = stp + (dw * 2 + (rs >> 3)) * 1024 + g * 128;
-                    *reinterpret_cast<uint16_t *>(rowp + (((kk >> 3) ^ g) << 4) + (kk & 7) * 2) = __ldg(p.ovals + cur);
+            // outliers of the strip inside this K step: every lane looks at its own buffered entry and
+            // writes the raw fp16 value over the zero-coded slot (after the warp's stores above)
+            __syncwarp();
+            for (;;) {
+                const int kk = (int)(buf_ent & 0xffffffu) - k0;   // entries are sorted: none is before k0
+                const bool in = kk < GM_BK;
+                if (in) {
+                    const int rs = (int)(buf_ent >> 24);
+                    unsigned char *rowp = stp + (dw * 2 + (rs >> 3)) * 1024 + (rs & 7) * 128;
+                    *reinterpret_cast<uint16_t *>(rowp + (((kk >> 3) ^ (rs & 7)) << 4) + (kk & 7) * 2) = (uint16_t)buf_val;
                 }
-                ++cur;
-                nent = cur < end ? __ldg(p.entries + cur) : 0x00ffffffu;
+                const int n_in = __popc(__ballot_sync(0xffffffffu, in));
+                if (n_in == 0) break;
+                cur += n_in;                                      // consumed: refill the buffer from there
+                buf_ent = cur + lane < end ? __ldg(p.entries + cur + lane) : 0x00ffffffu;
+                buf_val = cur + lane < end ? (uint32_t)__ldg(p.ovals + cur + lane) : 0u;
+                if (n_in < 32) break;                             // the run of this step ended inside the buffer
             }
             fence_async_smem();  // make the generic-proxy writes visible to the tensor core's reads
-            mbar_arrive(aready_bar(s));
+            mbar_arrive(aready_bar(sa));
         }
         if (!ok) *s_abort = 1;
 
@@ -310,7 +341,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         if (mbar_wait(accfull_bar, 0) && !*s_abort) {
             tcgen05_fence_after();
             const int q = warp & 3;              // the TMEM lane quarter this warp may read
-            const int half = (warp - 2) >> 2;    // two warps share a quarter: columns [0,128) and [128,256)
+            const int half = (warp - GM_CTRL_WARPS) >> 2;   // two warps share a quarter: columns [0,128) and [128,256)
             const int n = n0 + q * 32 + lane;
             const float bv = (p.bias && n < p.n_rows) ? __half2float(__ushort_as_half(__ldg(p.bias + n))) : 0.f;
             for (int c = half * (GM_BN / 64); c < (half + 1) * (GM_BN / 64); ++c) {

@@ -428,6 +428,8 @@ def main():
     ap.add_argument("--layers", type=int, default=LLAMA7B["layers"],
                     help="decoder layers in the pass (default: the full 32; smaller only for profiler captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch the pass directly instead of replaying a graph")
+    ap.add_argument("--only", default=None, choices=["gemm", "quantize"],
+                    help="run just one of the secondary measurements and print it (for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     global NO_GRAPH
@@ -437,6 +439,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.only:
+        torch.cuda.set_device(local_rank)
+        fn = measure_gemm if args.only == "gemm" else measure_quantize
+        print(json.dumps({args.only: fn(args.steps, args.warmup)}), flush=True)
         return
     run_ours(args, rank, world, local_rank)
 
