@@ -22,7 +22,7 @@
 //               TMEM) four times per step and commits the slot's `mma_done` mbarrier (which frees
 //               both the activation and the weight slot); after the last step it commits `acc_full`
 //   warps 3-10  epilogue: tcgen05.ld of their TMEM lane quarter (two warps per quarter, half of
-//               the columns each), + bias, convert, store y
+//               the columns each), + bias, convert, transpose through shared memory, 16-byte stores
 // Every mbarrier wait is bounded; if one runs out the CTA sets the caller's status word,
 // skips the rest of its work, frees its TMEM and returns.
 //
@@ -42,8 +42,8 @@ constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_WARPS) * 32;
 constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
 constexpr int GM_BN = 256;  // tokens per CTA = UMMA N
 constexpr int GM_BK = 64;   // K per pipeline step (one 128-byte swizzle row of fp16)
-constexpr int GM_XS = 3;    // activation / weight-tile ring depth
-constexpr int GM_CS = 8;    // code ring depth
+constexpr int GM_XS = 4;    // activation / weight-tile ring depth
+constexpr int GM_CS = 4;    // code ring depth
 constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2;  // 16 KB fp16 weight tile
 constexpr uint32_t B_BYTES = GM_BN * GM_BK * 2;  // 32 KB fp16 activation tile
 constexpr uint32_t C_BYTES = GM_BM * GM_BK;      // 8 KB code tile
@@ -337,30 +337,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         }
         if (!ok) *s_abort = 1;
 
-        // epilogue: TMEM lane = output feature, column = token
+        // epilogue: TMEM lane = output feature, column = token.  The accumulators go through shared
+        // memory (the rings are idle by now) so that y is written in 16-byte pieces along a token row.
         if (mbar_wait(accfull_bar, 0) && !*s_abort) {
             tcgen05_fence_after();
-            const int q = warp & 3;              // the TMEM lane quarter this warp may read
+            const int q = warp & 3;                         // the TMEM lane quarter this warp may read
             const int half = (warp - GM_CTRL_WARPS) >> 2;   // two warps share a quarter: columns [0,128) and [128,256)
-            const int n = n0 + q * 32 + lane;
+            const int nl = q * 32 + lane;                   // feature inside the tile
+            const int n = n0 + nl;
             const float bv = (p.bias && n < p.n_rows) ? __half2float(__ushort_as_half(__ldg(p.bias + n))) : 0.f;
+            // staging tile: [256 tokens][128 features + 8] 16-bit values (the pad keeps the column writes
+            // of a warp on distinct banks); it reuses the activation ring
+            uint16_t *stage = reinterpret_cast<uint16_t *>(base_ptr + OFF_B);
+            constexpr int ST = GM_BM + 8;
             for (int c = half * (GM_BN / 64); c < (half + 1) * (GM_BN / 64); ++c) {
                 if (m0 + c * 32 >= p.m) break;  // warp-uniform: no tokens left in this tile
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
                 tmem_ld_wait();
-                if (n < p.n_rows) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int m = m0 + c * 32 + j;
-                        if (m < p.m) {
-                            const float f = __uint_as_float(v[j]) + bv;
-                            if (p.out_bf16)
-                                reinterpret_cast<__nv_bfloat16 *>(p.y)[(int64_t)m * p.ldy + n] = __float2bfloat16_rn(f);
-                            else
-                                reinterpret_cast<__half *>(p.y)[(int64_t)m * p.ldy + n] = __float2half_rn(f);
-                        }
-                    }
+                for (int j = 0; j < 32; ++j) {
+                    const float f = __uint_as_float(v[j]) + bv;
+                    stage[(c * 32 + j) * ST + nl] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f))
+                                                               : __half_as_ushort(__float2half_rn(f));
+                }
+            }
+            // all eight epilogue warps have staged their part
+            asm volatile("bar.sync 1, %0;" ::"n"(GM_DQ_WARPS * 32) : "memory");
+            const int et = tid - GM_CTRL_WARPS * 32;         // 0..255
+            const int rows_left = min(GM_BN, p.m - m0);
+            const bool vec_ok = (n0 + GM_BM <= p.n_rows) && (p.ldy % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
+            for (int idx = et; idx < rows_left * (GM_BM / 8); idx += GM_DQ_WARPS * 32) {
+                const int row = idx >> 4, piece = idx & 15;  // 16 pieces of 8 features per token row
+                const uint16_t *src = stage + row * ST + piece * 8;
+                uint16_t *dst = reinterpret_cast<uint16_t *>(p.y) + (int64_t)(m0 + row) * p.ldy + n0 + piece * 8;
+                if (vec_ok) {
+                    *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
+                } else {
+                    for (int e = 0; e < 8; ++e)
+                        if (n0 + piece * 8 + e < p.n_rows) dst[e] = src[e];
                 }
             }
         } else {
