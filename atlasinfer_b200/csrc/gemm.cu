@@ -38,7 +38,8 @@ namespace {
 
 constexpr int GM_DQ_WARPS = 8;                       // dequantizer / epilogue warps (one 16-row strip each)
 constexpr int GM_CTRL_WARPS = 3;                     // activation producer, MMA issuer, code producer
-constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_WARPS) * 32;
+constexpr int GM_DQ_GROUPS = 2;                      // groups of dequantizer warps taking K steps in turn
+constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_GROUPS * GM_DQ_WARPS) * 32;
 constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
 constexpr int GM_BN = 256;  // tokens per CTA = UMMA N
 constexpr int GM_BK = 64;   // K per pipeline step (one 128-byte swizzle row of fp16)
@@ -260,7 +261,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         }
     } else {
         // ------------------------------ dequantizers, then epilogue ------------------------------
-        const int dw = warp - GM_CTRL_WARPS;   // 0..7: strip dw of the 128-row tile
+        const int dw = (warp - GM_CTRL_WARPS) % GM_DQ_WARPS;   // 0..7: strip dw of the 128-row tile
+        const int grp = (warp - GM_CTRL_WARPS) / GM_DQ_WARPS;  // this group rebuilds the steps it == grp (mod groups)
         const int g = lane >> 2, tig = lane & 3;
         const int bpr = p.n_cols / p.bs;
         const uint16_t *sc_tile = p.scales_t + (int64_t)blockIdx.x * bpr * 128;
@@ -274,7 +276,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         uint32_t buf_val = cur + lane < end ? (uint32_t)__ldg(p.ovals + cur + lane) : 0u;
         const uint32_t sw0 = (uint32_t)((2 * tig) ^ g) << 4, sw1 = (uint32_t)((2 * tig + 1) ^ g) << 4;  // swizzled 16-byte chunks
         bool ok = true;
-        for (int it = 0; it < KT && ok; ++it) {
+        for (int it = grp; it < KT && ok; it += GM_DQ_GROUPS) {
             const int sc_ = it % GM_CS, cround = it / GM_CS;   // code slot
             const int sa = it % GM_XS, around = it / GM_XS;    // weight-tile slot
             if (!mbar_wait(full_c(sc_), cround & 1) || *s_abort) { ok = false; break; }
@@ -318,9 +320,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
             // writes the raw fp16 value over the zero-coded slot (after the warp's stores above)
             __syncwarp();
             for (;;) {
-                const int kk = (int)(buf_ent & 0xffffffu) - k0;   // entries are sorted: none is before k0
+                const int kk = (int)(buf_ent & 0xffffffu) - k0;   // < 0: belongs to a step of another group
                 const bool in = kk < GM_BK;
-                if (in) {
+                const bool mine = in && kk >= 0;
+                if (mine) {
                     const int rs = (int)(buf_ent >> 24);
                     unsigned char *rowp = stp + (dw * 2 + (rs >> 3)) * 1024 + (rs & 7) * 128;
                     *reinterpret_cast<uint16_t *>(rowp + (((kk >> 3) ^ (rs & 7)) << 4) + (kk & 7) * 2) = (uint16_t)buf_val;
@@ -339,7 +342,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
 
         // epilogue: TMEM lane = output feature, column = token.  The accumulators go through shared
         // memory (the rings are idle by now) so that y is written in 16-byte pieces along a token row.
-        if (mbar_wait(accfull_bar, 0) && !*s_abort) {
+        if (grp != 0) {
+            // only the first group drains the accumulators
+        } else if (mbar_wait(accfull_bar, 0) && !*s_abort) {
             tcgen05_fence_after();
             const int q = warp & 3;                         // the TMEM lane quarter this warp may read
             const int half = (warp - GM_CTRL_WARPS) >> 2;   // two warps share a quarter: columns [0,128) and [128,256)
