@@ -286,6 +286,81 @@ def measure_quantize(steps, warmup):
     return nbytes * steps / secs / 1e9
 
 
+def measure_tp70b(rank, world, steps, warmup, barrier):
+    """Config 5: Llama-3-70B-shaped decode, batch 32, column-parallel over `world` ranks.
+
+    Every rank owns rows [r*N/g, (r+1)*N/g) of each linear (8 distinct layers, cycled ten times to
+    stand for the 80 layers; one layer's shards already exceed L2 together with the gathers) and
+    all-gathers its [32, N/g] output shard over NCCL.  Returns ms per token with and without the
+    gathers, and the aggregate algorithmic GB/s of the weight streaming.
+    """
+    import torch.distributed as dist
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(777 + rank)
+    layers, reps, m = 8, 10, 32
+    model = build_model(LLAMA70B_LINEARS, layers, gen, 0.015, rows_slice=(rank, world))
+    xs = {k: torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16) for k in {l.k for _, l in model}}
+    gathered = {l.n: torch.empty(world * m, l.n, dtype=torch.bfloat16, device=dev) for _, l in model}
+
+    def one_pass(gather):
+        for _ in range(reps):
+            for _, lin in model:
+                y = lin.forward(xs[lin.k], "gemv")
+                if gather and world > 1:
+                    dist.all_gather_into_tensor(gathered[lin.n], y)
+
+    out = {}
+    for name, gather in (("with_allgather", True), ("gemv_only", False)):
+        fn = lambda: one_pass(gather)  # noqa: E731
+        try:
+            graph = capture_graph(fn)
+            run = graph.replay
+            mode = "graph"
+        except Exception:  # noqa: BLE001 - capture of the collective not available: launch directly
+            torch.cuda.synchronize()
+            run, mode = fn, "eager"
+        secs = time_steps(run, steps, warmup, barrier)
+        t = torch.tensor([secs], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name] = dict(ms_per_token=float(t.item()) / steps * 1e3, launch=mode)
+    nbytes = sum(linear_bytes(l.n, l.k, l.n_out, m) for _, l in model) * reps
+    tot = torch.tensor([float(nbytes)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tot)
+    out["aggregate_gbs_with_allgather"] = float(tot.item()) / (out["with_allgather"]["ms_per_token"] * 1e-3) / 1e9
+    out["aggregate_gbs_gemv_only"] = float(tot.item()) / (out["gemv_only"]["ms_per_token"] * 1e-3) / 1e9
+    out["config"] = "llama3-70b-shaped linears, 80 layers (8 distinct x 10), batch 32 bf16, rows sharded over %d ranks" % world
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_quantize_sharded(rank, world, steps, warmup, barrier):
+    """Whole-model quantization sharded by layer: every rank quantizes whole layers of its own
+    (one 70B-shaped layer per step here), no collective.  Aggregate algorithmic GB/s."""
+    import torch.distributed as dist
+    import atlasinfer_b200 as ab
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(4242 + rank)
+    ws = [synth_weight(n, k, gen, 0.015) for _, n, k in LLAMA70B_LINEARS]
+    nbytes = 0
+    for w in ws:
+        q = ab.quantize_tensor(w)
+        n_out = q.fp16_outliers.numel()
+        nbytes += 2 * w.numel() + (w.numel() - n_out) + (w.numel() // BLOCK) * 2 + n_out * 10
+
+    def one():
+        for w in ws:
+            ab.quantize_tensor(w)
+
+    secs = time_steps(one, steps, warmup, barrier)
+    t = torch.tensor([secs], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return world * nbytes * steps / float(t.item()) / 1e9
+
+
 def cpu_linear_pass(linears, m, threads_note=True):
     """One pass of the CPU oracle port over `linears` [(n, k)]: dequantize + fp32 product per call.
     Returns (algorithmic bytes, seconds).  Weights are quantized (untimed) by the oracle first."""
@@ -383,6 +458,15 @@ def run_ours(args, rank, world, local_rank):
             extra[f"gemv_m{m}_gbs"] = b * max(2, args.steps // 2) / s / 1e9
     del model
     torch.cuda.empty_cache()
+    if world > 1 and not args.headline_only:
+        try:
+            tp = measure_tp70b(rank, world, max(2, args.steps // 5), 3, barrier)
+            qs = measure_quantize_sharded(rank, world, 2, 1, barrier)
+            if rank == 0:
+                extra["tp70b_decode"] = tp
+                extra["quantize_layer_sharded_gbs"] = qs
+        except Exception as e:  # noqa: BLE001 - keep the headline line
+            extra["tp70b_error"] = repr(e)
     if rank == 0 and not args.headline_only:
         try:
             extra["prefill_gemm_tflops"] = measure_gemm(max(2, args.steps // 4), 3)
