@@ -424,6 +424,7 @@ def run_ours(args, rank, world, local_rank):
     _capi.load()  # fail here, loudly, if the CUDA library is missing
     barrier = None
     if world > 1:
+        os.environ["NCCL_DEBUG"] = os.environ.get("ATLAS_NCCL_DEBUG", "WARN")  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
         barrier = dist.barrier
     pk = peaks()
