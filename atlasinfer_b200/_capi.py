@@ -67,7 +67,7 @@ def load() -> ctypes.CDLL:
     L.atlas_qlinear_gemv.restype = i32
     L.atlas_qlinear_gemv.argtypes = lin + [vp, vp]
     L.atlas_qlinear_gemm_workspace_bytes.restype = sz
-    L.atlas_qlinear_gemm_workspace_bytes.argtypes = [i64, i64]
+    L.atlas_qlinear_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     L.atlas_qlinear_gemm.restype = i32
     L.atlas_qlinear_gemm.argtypes = lin + [vp, sz, vp, vp]
     _lib = L

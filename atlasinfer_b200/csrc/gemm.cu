@@ -41,18 +41,24 @@ constexpr int GM_CTRL_WARPS = 3;                     // activation producer, MMA
 constexpr int GM_DQ_GROUPS = 2;                      // groups of dequantizer warps taking K steps in turn
 constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_GROUPS * GM_DQ_WARPS) * 32;
 constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
-constexpr int GM_BN = 256;  // tokens per CTA = UMMA N
 constexpr int GM_BK = 64;   // K per pipeline step (one 128-byte swizzle row of fp16)
 constexpr int GM_XS = 4;    // activation / weight-tile ring depth
 constexpr int GM_CS = 4;    // code ring depth
 constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2;  // 16 KB fp16 weight tile
-constexpr uint32_t B_BYTES = GM_BN * GM_BK * 2;  // 32 KB fp16 activation tile
 constexpr uint32_t C_BYTES = GM_BM * GM_BK;      // 8 KB code tile
 constexpr uint32_t S_BYTES = 256;                // one scale block: 128 rows x fp16
-constexpr uint32_t OFF_A = 0, OFF_B = GM_XS * A_BYTES, OFF_C = OFF_B + GM_XS * B_BYTES, OFF_BAR = OFF_C + GM_CS * C_BYTES;
-constexpr uint32_t OFF_S = OFF_BAR + 256;
-constexpr uint32_t GM_SMEM = OFF_S + GM_CS * S_BYTES + 1024 /*alignment slack*/;
-constexpr uint32_t TMEM_COLS = 256;
+// shared-memory map for a tile of BN tokens (BN = 32, 64, 128 or 256 = UMMA N)
+template <int BN>
+struct Smem {
+    static constexpr uint32_t B_BYTES = BN * GM_BK * 2;   // fp16 activation tile
+    static constexpr uint32_t OFF_A = 0;
+    static constexpr uint32_t OFF_B = GM_XS * A_BYTES;
+    static constexpr uint32_t OFF_C = OFF_B + GM_XS * B_BYTES;
+    static constexpr uint32_t OFF_BAR = OFF_C + GM_CS * C_BYTES;
+    static constexpr uint32_t OFF_S = OFF_BAR + 256;
+    static constexpr uint32_t TOTAL = OFF_S + GM_CS * S_BYTES + 1024 /*alignment slack*/;
+    static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+};
 constexpr int GM_SPIN_LIMIT = 1 << 20;
 
 // ---- PTX wrappers ----------------------------------------------------------------
@@ -136,7 +142,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 }
 // Instruction descriptor, kind::f16: D fp32 (1 at bit 4), A and B fp16 (0 at bits 7 and 10),
 // both K-major (0 at bits 15, 16), N >> 3 at bit 17, M >> 4 at bit 24.
-constexpr uint32_t GM_IDESC = (1u << 4) | ((uint32_t)(GM_BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
+template <int BN>
+constexpr uint32_t gm_idesc() { return (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24); }
 
 // Four biased codes -> two half2 of fp16(fp16(code) * scale), as in the streaming kernel.
 __device__ __forceinline__ void dequant4(uint32_t w, __half2 scale2, uint32_t &lo, uint32_t &hi) {
@@ -166,11 +173,17 @@ struct GemmParams {
     int n_chunks;
     int bs_tiles;   // k-tiles per scale block when block_size % 64 == 0 (scales staged by the producer), else 0
     int out_bf16;
+    int splits;        // K slices (grid.z); > 1: fp32 partial tiles go to `partials`, a second kernel adds them
+    float *partials;   // [splits][m][n_rows] fp32
     int *error_flag;
 };
 
+template <int BN>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
+    using SM = Smem<BN>;
+    constexpr uint32_t B_BYTES = SM::B_BYTES, OFF_A = SM::OFF_A, OFF_B = SM::OFF_B, OFF_C = SM::OFF_C, OFF_BAR = SM::OFF_BAR,
+                       OFF_S = SM::OFF_S, TMEM_COLS = SM::TMEM_COLS;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;          // operand tiles need 1024-byte alignment
@@ -187,8 +200,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * GM_BM;  // first weight row (output feature) of the tile
-    const int m0 = blockIdx.y * GM_BN;  // first token
-    const int KT = p.k_tiles;
+    const int m0 = blockIdx.y * BN;  // first token
+    // this CTA's K steps (grid.z slices K)
+    const int kt_begin = (int)((long long)p.k_tiles * blockIdx.z / p.splits);
+    const int KT = (int)((long long)p.k_tiles * (blockIdx.z + 1) / p.splits) - kt_begin;
 
     if (tid == 0) {
         for (int s = 0; s < GM_XS; ++s) {
@@ -222,13 +237,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
                 if (round > 0 && !mbar_wait(mma_done(s), (round - 1) & 1)) { *s_abort = 1; break; }
                 if (*s_abort) break;
                 mbar_arrive_expect_tx(full_x(s), B_BYTES);
-                tma_load_2d(base + OFF_B + s * B_BYTES, &x_map, it * GM_BK, m0, full_x(s));
+                tma_load_2d(base + OFF_B + s * B_BYTES, &x_map, (kt_begin + it) * GM_BK, m0, full_x(s));
             }
         }
     } else if (warp == 2) {
         // ------------------------------ code producer ------------------------------
         if (lane == 0) {
-            const uint8_t *ctile = p.tiles + (size_t)blockIdx.x * KT * C_BYTES;
+            const uint8_t *ctile = p.tiles + ((size_t)blockIdx.x * p.k_tiles + kt_begin) * C_BYTES;
             const int bpr = p.n_cols / p.bs;
             for (int it = 0; it < KT; ++it) {
                 const int s = it % GM_CS, round = it / GM_CS;
@@ -238,7 +253,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
                 bulk_load_1d(base + OFF_C + s * C_BYTES, ctile + (size_t)it * C_BYTES, C_BYTES, full_c(s));
                 if (p.bs_tiles)
                     bulk_load_1d(base + OFF_S + s * S_BYTES,
-                                 p.scales_t + ((size_t)blockIdx.x * bpr + it / p.bs_tiles) * 128, S_BYTES, full_c(s));
+                                 p.scales_t + ((size_t)blockIdx.x * bpr + (kt_begin + it) / p.bs_tiles) * 128, S_BYTES, full_c(s));
             }
         }
     } else if (warp == 1) {
@@ -253,7 +268,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
                 const uint64_t da = make_smem_desc(base + OFF_A + s * A_BYTES), db = make_smem_desc(base + OFF_B + s * B_BYTES);
 #pragma unroll
                 for (int k = 0; k < GM_BK / 16; ++k)  // 32 bytes (16 fp16) further along K per step
-                    umma_f16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), GM_IDESC, (it | k) != 0);
+                    umma_f16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), gm_idesc<BN>(), (it | k) != 0);
                 umma_commit(mma_done(s));  // arrives when these MMAs have finished reading both slots
             }
             if (!ok) *s_abort = 1;
@@ -269,8 +284,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         const int r0 = dw * 16 + g, r1 = r0 + 8;   // the two rows of the tile this thread rebuilds in every K step
         // outlier cursor of the strip (its list is sorted by column)
         const int64_t strip = (int64_t)blockIdx.x * 8 + dw;
-        int cur = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1));
-        const int end = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + p.n_chunks);
+        int cur = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + kt_begin);
+        const int end = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + kt_begin + KT);
         // the warp keeps the next 32 entries of the list in registers, one per lane
         uint32_t buf_ent = cur + lane < end ? __ldg(p.entries + cur + lane) : 0x00ffffffu;
         uint32_t buf_val = cur + lane < end ? (uint32_t)__ldg(p.ovals + cur + lane) : 0u;
@@ -281,7 +296,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
             const int sa = it % GM_XS, around = it / GM_XS;    // weight-tile slot
             if (!mbar_wait(full_c(sc_), cround & 1) || *s_abort) { ok = false; break; }
             const unsigned char *codes = base_ptr + OFF_C + sc_ * C_BYTES + (dw * 2 * 32 + lane) * 16;
-            const int k0 = it * GM_BK;
+            const int k0 = (kt_begin + it) * GM_BK;
             const uint4 c0 = *reinterpret_cast<const uint4 *>(codes);          // row r0, k 16*tig .. +15
             const uint4 c1 = *reinterpret_cast<const uint4 *>(codes + 512);    // row r1
             __half sh0, sh1;
@@ -351,36 +366,59 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
             const int nl = q * 32 + lane;                   // feature inside the tile
             const int n = n0 + nl;
             const float bv = (p.bias && n < p.n_rows) ? __half2float(__ushort_as_half(__ldg(p.bias + n))) : 0.f;
-            // staging tile: [256 tokens][128 features + 8] 16-bit values (the pad keeps the column writes
-            // of a warp on distinct banks); it reuses the activation ring
-            uint16_t *stage = reinterpret_cast<uint16_t *>(base_ptr + OFF_B);
-            constexpr int ST = GM_BM + 8;
-            for (int c = half * (GM_BN / 64); c < (half + 1) * (GM_BN / 64); ++c) {
+            // staging tile [BN tokens][128 features (+ pad)] in the idle rings: 16-bit outputs, or fp32
+            // partial sums when K is split between CTAs
+            const bool partial = p.splits > 1;
+            unsigned char *stage = base_ptr + OFF_A;
+            const int st_bytes = partial ? (GM_BM + 4) * 4 : (GM_BM + 8) * 2;   // row stride; pads keep banks apart
+            for (int c = half; c < BN / 32; c += 2) {
                 if (m0 + c * 32 >= p.m) break;  // warp-uniform: no tokens left in this tile
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    const float f = __uint_as_float(v[j]) + bv;
-                    stage[(c * 32 + j) * ST + nl] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f))
-                                                               : __half_as_ushort(__float2half_rn(f));
+                    unsigned char *row = stage + (size_t)(c * 32 + j) * st_bytes;
+                    if (partial) {
+                        reinterpret_cast<uint32_t *>(row)[nl] = v[j];
+                    } else {
+                        const float f = __uint_as_float(v[j]) + bv;
+                        reinterpret_cast<uint16_t *>(row)[nl] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f))
+                                                                          : __half_as_ushort(__float2half_rn(f));
+                    }
                 }
             }
             // all eight epilogue warps have staged their part
             asm volatile("bar.sync 1, %0;" ::"n"(GM_DQ_WARPS * 32) : "memory");
             const int et = tid - GM_CTRL_WARPS * 32;         // 0..255
-            const int rows_left = min(GM_BN, p.m - m0);
-            const bool vec_ok = (n0 + GM_BM <= p.n_rows) && (p.ldy % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
-            for (int idx = et; idx < rows_left * (GM_BM / 8); idx += GM_DQ_WARPS * 32) {
-                const int row = idx >> 4, piece = idx & 15;  // 16 pieces of 8 features per token row
-                const uint16_t *src = stage + row * ST + piece * 8;
-                uint16_t *dst = reinterpret_cast<uint16_t *>(p.y) + (int64_t)(m0 + row) * p.ldy + n0 + piece * 8;
-                if (vec_ok) {
-                    *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
-                } else {
-                    for (int e = 0; e < 8; ++e)
-                        if (n0 + piece * 8 + e < p.n_rows) dst[e] = src[e];
+            const int rows_left = min(BN, p.m - m0);
+            if (partial) {
+                // fp32 partial tile -> partials[z][m][n], 16 bytes (4 features) per thread and store
+                float *dst0 = p.partials + (size_t)blockIdx.z * p.m * p.n_rows;
+                const bool vec_ok = (n0 + GM_BM <= p.n_rows) && (p.n_rows % 4 == 0);
+                for (int idx = et; idx < rows_left * (GM_BM / 4); idx += GM_DQ_WARPS * 32) {
+                    const int row = idx >> 5, piece = idx & 31;
+                    const float *src = reinterpret_cast<const float *>(stage + (size_t)row * st_bytes) + piece * 4;
+                    float *dst = dst0 + (size_t)(m0 + row) * p.n_rows + n0 + piece * 4;
+                    if (vec_ok) {
+                        *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(src);
+                    } else {
+                        for (int e = 0; e < 4; ++e)
+                            if (n0 + piece * 4 + e < p.n_rows) dst[e] = src[e];
+                    }
+                }
+            } else {
+                const bool vec_ok = (n0 + GM_BM <= p.n_rows) && (p.ldy % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
+                for (int idx = et; idx < rows_left * (GM_BM / 8); idx += GM_DQ_WARPS * 32) {
+                    const int row = idx >> 4, piece = idx & 15;  // 16 pieces of 8 features per token row
+                    const uint16_t *src = reinterpret_cast<const uint16_t *>(stage + (size_t)row * st_bytes) + piece * 8;
+                    uint16_t *dst = reinterpret_cast<uint16_t *>(p.y) + (int64_t)(m0 + row) * p.ldy + n0 + piece * 8;
+                    if (vec_ok) {
+                        *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
+                    } else {
+                        for (int e = 0; e < 8; ++e)
+                            if (n0 + piece * 8 + e < p.n_rows) dst[e] = src[e];
+                    }
                 }
             }
         } else {
@@ -394,6 +432,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     if (tid == 0 && *s_abort && p.error_flag) atomicExch(p.error_flag, 1);
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Adds the K-slice partial tiles in slice order (deterministic), adds the bias and writes y.
+__global__ void __launch_bounds__(256)
+gemm_finish_kernel(const float *partials, int splits, int m, int n_rows, const uint16_t *bias, void *y, int64_t ldy,
+                   int out_bf16) {
+    const int64_t total = (int64_t)m * n_rows;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int row = (int)(i / n_rows), n = (int)(i - (int64_t)row * n_rows);
+        float acc = 0.f;
+        for (int z = 0; z < splits; ++z) acc += partials[(size_t)z * total + i];
+        if (bias) acc += __half2float(__ushort_as_half(__ldg(bias + n)));
+        if (out_bf16) reinterpret_cast<__nv_bfloat16 *>(y)[(int64_t)row * ldy + n] = __float2bfloat16_rn(acc);
+        else reinterpret_cast<__half *>(y)[(int64_t)row * ldy + n] = __float2half_rn(acc);
     }
 }
 
@@ -441,9 +494,60 @@ constexpr size_t GM_WS_HEADER = 256;  // reserved; the fp16 copy of x follows
 }  // namespace
 }  // namespace atlas
 
-extern "C" size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_cols) {
-    if (m <= 0 || n_cols <= 0) return atlas::GM_WS_HEADER;
-    return atlas::GM_WS_HEADER + (size_t)m * (size_t)n_cols * 2;
+namespace atlas {
+namespace {
+
+// tokens per tile for a batch of m rows
+int gemm_bn_for(int64_t m) { return m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
+
+// K slices: enough CTAs to occupy the SMs when the output has few tiles (decode-sized batches only)
+int gemm_splits_for(int64_t m, int64_t n_rows, int64_t n_cols, int sms) {
+    const int bn = gemm_bn_for(m);
+    if (bn > 64) return 1;
+    const int64_t tiles = ceil_div_i64(n_rows, GM_BM) * ceil_div_i64(m, bn);
+    int splits = 1;
+    const int k_tiles = (int)(n_cols / 64);
+    while (splits < 8 && tiles * splits < sms && k_tiles / (splits * 2) >= 8) splits *= 2;
+    return splits;
+}
+
+int gemm_sm_count() {
+    static thread_local int dev_cached = -1, sms = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != dev_cached) {
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+        dev_cached = dev;
+    }
+    return sms;
+}
+
+template <int BN>
+int launch_gemm(const CUtensorMap &x_map, const GemmParams &p, cudaStream_t st) {
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        int rc = check_cuda(cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)Smem<BN>::TOTAL), "cudaFuncSetAttribute(gemm smem)");
+        if (rc) return rc;
+        configured_dev = dev;
+    }
+    dim3 grid((unsigned)ceil_div_i64(p.n_rows, GM_BM), (unsigned)ceil_div_i64(p.m, BN), (unsigned)p.splits);
+    gemm_kernel<BN><<<grid, GM_THREADS, Smem<BN>::TOTAL, st>>>(x_map, p);
+    return check_cuda(cudaGetLastError(), "gemm_kernel launch");
+}
+
+}  // namespace
+}  // namespace atlas
+
+extern "C" size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_rows, int64_t n_cols) {
+    if (m <= 0 || n_cols <= 0 || n_rows <= 0) return atlas::GM_WS_HEADER;
+    // fp16 copy of x (bf16 or strided input), then room for up to 8 fp32 K-slice partial outputs
+    // (only decode-sized batches are ever sliced)
+    const size_t xcopy = ((size_t)m * (size_t)n_cols * 2 + 255) & ~(size_t)255;
+    const size_t part = atlas::gemm_bn_for(m) <= 64 ? (size_t)8 * (size_t)m * (size_t)n_rows * 4 : 0;
+    return atlas::GM_WS_HEADER + xcopy + part;
 }
 
 extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
@@ -468,18 +572,19 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
                     "atlas_qlinear_gemm: too large");
     ATLAS_RETURN_IF(((uintptr_t)tiles & 15) != 0 || ((uintptr_t)workspace & 255) != 0, ATLAS_ERR_BAD_ARGUMENT,
                     "atlas_qlinear_gemm: tiles must be 16-byte and workspace 256-byte aligned");
-    const size_t need = atlas_qlinear_gemm_workspace_bytes(m, n_cols);
+    const size_t need = atlas_qlinear_gemm_workspace_bytes(m, n_rows, n_cols);
     ATLAS_RETURN_IF(workspace_bytes < need, ATLAS_ERR_CAPACITY,
                     "atlas_qlinear_gemm: workspace holds %zu bytes, %zu needed", workspace_bytes, need);
     int rc = check_device();
     if (rc) return rc;
     if (m == 0) return ATLAS_OK;
     cudaStream_t st = (cudaStream_t)stream;
-
+    const int bn = gemm_bn_for(m);
 
     // operand B must be fp16 with rows on 16-byte boundaries for the tensor map
     const void *xb = x;
     int64_t ldb = ldx;
+    const size_t xcopy = ((size_t)m * (size_t)n_cols * 2 + 255) & ~(size_t)255;
     const bool direct = dtype == ATLAS_DTYPE_F16 && ((uintptr_t)x & 15) == 0 && (ldx % 8) == 0;
     if (!direct) {
         uint16_t *xf = (uint16_t *)((char *)workspace + GM_WS_HEADER);
@@ -499,22 +604,12 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
     CUtensorMap x_map;
     const cuuint64_t gdim[2] = {(cuuint64_t)n_cols, (cuuint64_t)m};
     const cuuint64_t gstride[1] = {(cuuint64_t)ldb * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)GM_BK, (cuuint32_t)GM_BN};
+    const cuuint32_t box[2] = {(cuuint32_t)GM_BK, (cuuint32_t)bn};
     const cuuint32_t estride[2] = {1, 1};
     CUresult cr = encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(xb), gdim, gstride, box,
                          estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     ATLAS_RETURN_IF(cr != CUDA_SUCCESS, ATLAS_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)cr);
-
-    static thread_local int configured_dev = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_dev != dev) {
-        rc = check_cuda(cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GM_SMEM),
-                        "cudaFuncSetAttribute(gemm smem)");
-        if (rc) return rc;
-        configured_dev = dev;
-    }
 
     GemmParams p;
     p.tiles = tiles;
@@ -533,8 +628,22 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
     p.n_chunks = (int)(n_cols / 64);
     p.bs_tiles = block_size % 64 == 0 ? block_size / 64 : 0;
     p.out_bf16 = dtype == ATLAS_DTYPE_BF16;
+    p.splits = gemm_splits_for(m, n_rows, n_cols, gemm_sm_count());
+    p.partials = (float *)((char *)workspace + GM_WS_HEADER + xcopy);
     p.error_flag = status;
-    dim3 grid((unsigned)ceil_div_i64(n_rows, GM_BM), (unsigned)ceil_div_i64(m, GM_BN), 1);
-    gemm_kernel<<<grid, GM_THREADS, GM_SMEM, st>>>(x_map, p);
-    return check_cuda(cudaGetLastError(), "gemm_kernel launch");
+    switch (bn) {
+        case 32: rc = launch_gemm<32>(x_map, p, st); break;
+        case 64: rc = launch_gemm<64>(x_map, p, st); break;
+        case 128: rc = launch_gemm<128>(x_map, p, st); break;
+        default: rc = launch_gemm<256>(x_map, p, st); break;
+    }
+    if (rc) return rc;
+    if (p.splits > 1) {
+        const int64_t total = m * n_rows;
+        const int64_t blocks = ceil_div_i64(total, 256);
+        gemm_finish_kernel<<<(unsigned)(blocks < 2048 ? blocks : 2048), 256, 0, st>>>(
+            p.partials, p.splits, (int)m, (int)n_rows, (const uint16_t *)bias, y, ldy, p.out_bf16);
+        rc = check_cuda(cudaGetLastError(), "gemm_finish_kernel launch");
+    }
+    return rc;
 }

@@ -21,8 +21,8 @@ import torch.nn as nn
 from .. import _capi
 from ..quant.adaptive_quantizer import QuantizedTensor
 
-# rows of x up to which the HBM-bound GEMV kernel is used; above it the tcgen05 GEMM
-GEMV_MAX_ROWS = 32
+# rows of x up to which the CUDA-core-issued streaming kernel is used; above it the tcgen05 kernel
+GEMV_MAX_ROWS = 8
 
 _VERBOSE = os.environ.get("ATLAS_VERBOSE", "0") not in ("", "0")
 
@@ -138,7 +138,7 @@ def quantized_linear_forward(x: torch.Tensor, layout: KernelLayout, bias: Option
             status = L.atlas_qlinear_gemv(*args, flag, _capi.stream_ptr(dev))
             _capi.check(status, "atlas_qlinear_gemv")
         else:
-            ws_bytes = int(L.atlas_qlinear_gemm_workspace_bytes(m, k))
+            ws_bytes = int(L.atlas_qlinear_gemm_workspace_bytes(m, n, k))
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
             status = L.atlas_qlinear_gemm(*args, ws.data_ptr(), ws_bytes, flag, _capi.stream_ptr(dev))
             _capi.check(status, "atlas_qlinear_gemm")

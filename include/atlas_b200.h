@@ -165,11 +165,13 @@ ATLAS_API int atlas_repack(const int8_t *codes, int64_t n_codes, const void *out
  * dependent launch: only weights are read before the stream's earlier work
  * has completed.
  *
- * atlas_qlinear_gemm: prefill shapes (m >= 128 intended, any m >= 1
- * accepted).  Stages tiles through shared memory, dequantises to fp16
- * operand tiles and multiplies with tcgen05 into TMEM accumulators.
- * `workspace` must hold atlas_qlinear_gemm_workspace_bytes(m, n_cols) bytes,
- * 256-byte aligned.
+ * atlas_qlinear_gemm: batches above 8 rows (any m >= 1 accepted).  Stages
+ * tiles through shared memory, dequantises to fp16 operand tiles and multiplies
+ * with tcgen05 into TMEM accumulators; the token tile is 32, 64, 128 or 256
+ * wide by m, and for decode-sized batches K is sliced over CTAs with the
+ * fp32 partial tiles added in slice order by a second kernel (deterministic).
+ * `workspace` must hold atlas_qlinear_gemm_workspace_bytes(m, n_rows, n_cols)
+ * bytes, 256-byte aligned.
  */
 ATLAS_API int atlas_qlinear_gemv(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
                                  const void *scales_tiled, const int32_t *outlier_chunk_ptr,
@@ -177,7 +179,7 @@ ATLAS_API int atlas_qlinear_gemv(const void *x, int dtype, int64_t m, int64_t ld
                                  int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y,
                                  int64_t ldy, int32_t *status, void *stream);
 
-ATLAS_API size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_cols);
+ATLAS_API size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_rows, int64_t n_cols);
 ATLAS_API int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
                                  const void *scales_tiled, const int32_t *outlier_chunk_ptr,
                                  const uint32_t *outlier_entries, const void *outlier_vals_sorted,

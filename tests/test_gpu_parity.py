@@ -192,6 +192,18 @@ def test_gemm_matches_oracle(m, dtype, cuda_device):
     assert rel_max_err(y, ref) < LINEAR_TOL
 
 
+@pytest.mark.parametrize("m", [1, 9, 16, 32, 33, 64, 100])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 8192), (200, 1024), (11008, 4096)])
+def test_gemm_small_batches_and_k_slices(m, n, k, cuda_device):
+    # decode-sized batches through the tcgen05 kernel: narrow token tiles, K sliced over CTAs
+    dtype = torch.bfloat16 if m % 2 else torch.float16
+    o, x, b, ref = _linear_case(n, k, m, dtype, 40 + m + n, bias=(m != 16))
+    y = _run_linear(o, x, b, cuda_device, "gemm")
+    assert rel_max_err(y, ref) < LINEAR_TOL
+    y2 = _run_linear(o, x, b, cuda_device, "gemm")
+    assert torch.equal(bits(y), bits(y2))  # slices are added in a fixed order
+
+
 def test_gemm_llama_prefill_shape(cuda_device):
     # 2048 tokens against 4096 x 4096; the reference product is evaluated on the GPU in fp32
     # from the oracle's dequantized weight (the CPU oracle's fp64 loop would take minutes here)
