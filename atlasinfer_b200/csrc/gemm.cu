@@ -182,6 +182,8 @@ template <int BN>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     using SM = Smem<BN>;
+    // the next kernel of the stream may start its own weight-only prologue right away
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr uint32_t B_BYTES = SM::B_BYTES, OFF_A = SM::OFF_A, OFF_B = SM::OFF_B, OFF_C = SM::OFF_C, OFF_BAR = SM::OFF_BAR,
                        OFF_S = SM::OFF_S, TMEM_COLS = SM::TMEM_COLS;
     extern __shared__ unsigned char smem_raw[];
@@ -232,6 +234,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     if (warp == 0) {
         // ------------------------------ activation producer ------------------------------
         if (lane == 0) {
+            // activations come from earlier kernels of the stream; everything else so far read only weights
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int it = 0; it < KT; ++it) {
                 const int s = it % GM_XS, round = it / GM_XS;
                 if (round > 0 && !mbar_wait(mma_done(s), (round - 1) & 1)) { *s_abort = 1; break; }
@@ -439,6 +443,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
 __global__ void __launch_bounds__(256)
 gemm_finish_kernel(const float *partials, int splits, int m, int n_rows, const uint16_t *bias, void *y, int64_t ldy,
                    int out_bf16) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t total = (int64_t)m * n_rows;
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
         const int row = (int)(i / n_rows), n = (int)(i - (int64_t)row * n_rows);
@@ -453,6 +459,8 @@ gemm_finish_kernel(const float *partials, int splits, int m, int n_rows, const u
 // bf16 -> fp16 (saturating) into a dense [m][k] buffer; also used to make strided fp16 rows dense.
 __global__ void __launch_bounds__(256)
 to_f16_kernel(const uint16_t *x, int64_t ldx, int m, int k, int from_bf16, uint16_t *out) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t total = (int64_t)m * (k >> 1);
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
         const int64_t row = i / (k >> 1), c2 = i - row * (k >> 1);
@@ -497,6 +505,21 @@ constexpr size_t GM_WS_HEADER = 256;  // reserved; the fp16 copy of x follows
 namespace atlas {
 namespace {
 
+// launch configuration with programmatic dependent launch allowed
+cudaLaunchConfig_t pdl_config(dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+    static thread_local cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cfg;
+}
+
 // tokens per tile for a batch of m rows
 int gemm_bn_for(int64_t m) { return m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
 
@@ -533,9 +556,9 @@ int launch_gemm(const CUtensorMap &x_map, const GemmParams &p, cudaStream_t st) 
         if (rc) return rc;
         configured_dev = dev;
     }
-    dim3 grid((unsigned)ceil_div_i64(p.n_rows, GM_BM), (unsigned)ceil_div_i64(p.m, BN), (unsigned)p.splits);
-    gemm_kernel<BN><<<grid, GM_THREADS, Smem<BN>::TOTAL, st>>>(x_map, p);
-    return check_cuda(cudaGetLastError(), "gemm_kernel launch");
+    cudaLaunchConfig_t cfg = pdl_config(dim3((unsigned)ceil_div_i64(p.n_rows, GM_BM), (unsigned)ceil_div_i64(p.m, BN), (unsigned)p.splits),
+                                        dim3(GM_THREADS), Smem<BN>::TOTAL, st);
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_kernel<BN>, x_map, p), "gemm_kernel launch");
 }
 
 }  // namespace
@@ -590,9 +613,9 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
         uint16_t *xf = (uint16_t *)((char *)workspace + GM_WS_HEADER);
         const int64_t pairs = m * (n_cols / 2);
         const int64_t blocks = ceil_div_i64(pairs, 256);
-        to_f16_kernel<<<(unsigned)(blocks < 65535 ? blocks : 65535), 256, 0, st>>>(
-            (const uint16_t *)x, ldx, (int)m, (int)n_cols, dtype == ATLAS_DTYPE_BF16, xf);
-        rc = check_cuda(cudaGetLastError(), "to_f16_kernel launch");
+        cudaLaunchConfig_t cfg = pdl_config(dim3((unsigned)(blocks < 65535 ? blocks : 65535)), dim3(256), 0, st);
+        rc = check_cuda(cudaLaunchKernelEx(&cfg, to_f16_kernel, (const uint16_t *)x, ldx, (int)m, (int)n_cols,
+                                           (int)(dtype == ATLAS_DTYPE_BF16), xf), "to_f16_kernel launch");
         if (rc) return rc;
         xb = xf;
         ldb = n_cols;
@@ -641,9 +664,9 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
     if (p.splits > 1) {
         const int64_t total = m * n_rows;
         const int64_t blocks = ceil_div_i64(total, 256);
-        gemm_finish_kernel<<<(unsigned)(blocks < 2048 ? blocks : 2048), 256, 0, st>>>(
-            p.partials, p.splits, (int)m, (int)n_rows, (const uint16_t *)bias, y, ldy, p.out_bf16);
-        rc = check_cuda(cudaGetLastError(), "gemm_finish_kernel launch");
+        cudaLaunchConfig_t cfg = pdl_config(dim3((unsigned)(blocks < 2048 ? blocks : 2048)), dim3(256), 0, st);
+        rc = check_cuda(cudaLaunchKernelEx(&cfg, gemm_finish_kernel, (const float *)p.partials, p.splits, (int)m, (int)n_rows,
+                                           (const uint16_t *)bias, y, ldy, p.out_bf16), "gemm_finish_kernel launch");
     }
     return rc;
 }
