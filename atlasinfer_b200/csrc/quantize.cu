@@ -20,6 +20,7 @@
 //   code  = int8(clamp(rint(fp16(x / scale)), -127, 127))    (:125-126)
 // The fp64 second moment is a two-pass sum here and a Welford recurrence in
 // ATen; both carry ~1e-16 relative error, far below the fp16 rounding step.
+#include <cmath>
 #include <mutex>
 
 #include "common.cuh"
@@ -323,6 +324,323 @@ __global__ void __launch_bounds__(QT_THREADS) quantize_kernel(QuantParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fast variant for block sizes 32 / 64 / 128 / 256 (EPT = block_size / 8 values per thread, kept
+// in registers).  Same results as quantize_kernel above, bit for bit, with most of the IEEE
+// divisions and all of the fp64 work moved off the common path:
+//   * the second moment is accumulated in fp32 (error <= ~1e-6 relative); only if rounding the
+//     standard deviation to fp16 could go either way within 4e-6 is it recomputed in fp64;
+//   * |fp16(d / den)| > thr is decided from d * (1 / den) against the real number at which the
+//     rounded quotient crosses thr, with a 2^-21 guard band inside which the exact quotient is used;
+//   * fp16(x / scale) is taken from x * (1 / scale) when nudging the product by 2^-22 either way
+//     rounds to the same fp16 number, else from the exact quotient.
+// Codes are written once, uncompacted, to shared memory by the threads that computed the block
+// statistics; the compaction pass only moves bytes.
+struct FastConsts {
+    float t_lo, t_hi;  // guard band around the |z| decision boundary
+    float thr_f;
+};
+
+template <int EPT>
+__global__ void __launch_bounds__(QT_THREADS, (EPT <= 16 ? 4 : 2)) quantize_fast_kernel(QuantParams p, FastConsts fc) {
+    constexpr int BS = EPT * 8;
+    constexpr int TILE_BLOCKS = QT_TILE / BS;
+    // Blocks are padded (16 bytes of values, 8 bytes of codes) so that the four blocks a warp works
+    // on at a time fall on different banks.
+    constexpr int XSTRIDE = BS * 2 + 16;  // bytes
+    constexpr int DSTRIDE = BS + 8;
+    __shared__ __align__(16) uint8_t s_xb[TILE_BLOCKS * XSTRIDE];
+    __shared__ __align__(16) uint8_t s_dense[TILE_BLOCKS * DSTRIDE];
+    auto xref = [&](int e) -> uint16_t & {
+        return *reinterpret_cast<uint16_t *>(s_xb + (e / BS) * XSTRIDE + (e % BS) * 2);
+    };
+    __shared__ __align__(16) uint8_t s_codes[QT_TILE + 32];
+    __shared__ uint32_t s_mask[QT_WORDS];
+    __shared__ uint32_t s_wordpre[QT_WORDS];
+    __shared__ uint16_t s_scale[TILE_BLOCKS];
+    __shared__ uint32_t s_warp_tot[QT_THREADS / 32];
+    __shared__ long long s_tile_prefix;
+    __shared__ int s_tile_total;
+    __shared__ unsigned int s_tile;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const uint16_t eps_h = f2h_bits(1e-6f);
+    const float eps_f = h2f_bits(eps_h);
+
+    for (;;) {
+        __syncthreads();  // previous tile's shared state is no longer read
+        if (tid == 0) s_tile = atomicAdd(p.tile_counter, 1u);
+        __syncthreads();
+        const int64_t tile = s_tile;
+        if (tile >= p.num_tiles) break;
+        const int64_t tile_base = tile * QT_TILE;
+        const int tile_elems = (int)min((int64_t)QT_TILE, p.padded - tile_base);
+        const int tile_real = (int)max((int64_t)0, min((int64_t)tile_elems, p.numel - tile_base));
+        const int tile_blocks = tile_elems / BS;
+
+        // ---- stage the tile (zero padding included) -------------------------------
+        if (p.in_aligned) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(p.x + tile_base);
+            for (int v = tid; v < QT_TILE / 8; v += QT_THREADS) {
+                int e0 = v * 8;
+                if (e0 + 8 <= tile_real) {
+                    *reinterpret_cast<uint4 *>(s_xb + (e0 / BS) * XSTRIDE + (e0 % BS) * 2) = __ldg(src + v);
+                } else if (e0 < tile_elems) {
+                    for (int e = e0; e < e0 + 8; ++e) xref(e) = (e < tile_real) ? p.x[tile_base + e] : (uint16_t)0;
+                }
+            }
+        } else {
+            for (int e = tid; e < tile_elems; e += QT_THREADS)
+                xref(e) = (e < tile_real) ? p.x[tile_base + e] : (uint16_t)0;
+        }
+        for (int w = tid; w < QT_WORDS; w += QT_THREADS) s_mask[w] = 0u;
+        __syncthreads();
+
+        // ---- phase A: statistics and codes of whole blocks, 8 threads per block ----------
+        {
+            const int l = tid & 7;    // ATen SIMD lane this thread plays
+            const int grp = tid >> 3;
+            const unsigned gmask = 0xffu << (lane & 24);
+            for (int b = grp; b < tile_blocks; b += QT_THREADS / 8) {
+                const uint16_t *xb = reinterpret_cast<const uint16_t *>(s_xb + b * XSTRIDE);
+                float f[EPT];
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) f[j] = h2f_bits(xb[j * 8 + l]);
+                // fp32 sum in ATen's order
+                float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) a4[j & 3] = __fadd_rn(a4[j & 3], f[j]);
+                const float lane_sum = __fadd_rn(__fadd_rn(__fadd_rn(a4[0], a4[1]), a4[2]), a4[3]);
+                float fin = 0.f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) fin = __fadd_rn(fin, __shfl_sync(gmask, lane_sum, s, 8));
+                const float mean32 = __fdiv_rn(fin, (float)BS);
+                const float mean_f = h2f_bits(f2h_bits(mean32));
+                // second moment: fp32 first
+                // (about mean32, with the first moment about it taken out again, so that the rounding
+                // of mean32 itself only enters to second order)
+                float m2f = 0.f, r1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) {
+                    const float d = f[j] - mean32;
+                    r1 += d;
+                    m2f = fmaf(d, d, m2f);
+                }
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) {
+                    m2f += __shfl_xor_sync(gmask, m2f, o, 8);
+                    r1 += __shfl_xor_sync(gmask, r1, o, 8);
+                }
+                m2f = fmaxf(fmaf(-r1, r1 * (1.f / (float)BS), m2f), 0.f);
+                const float std32 = __fsqrt_rn(__fdiv_rn(m2f, (float)(BS - 1)));
+                uint16_t std_h = f2h_bits(std32 * (1.f - 4e-6f));
+                if (std_h != f2h_bits(std32 * (1.f + 4e-6f))) {
+                    // the fp16 rounding is within reach of the fp32 error: redo it in fp64 (group-uniform)
+                    double dsum = 0.0;
+#pragma unroll
+                    for (int j = 0; j < EPT; ++j) dsum += (double)f[j];
+#pragma unroll
+                    for (int o = 1; o < 8; o <<= 1) dsum += __shfl_xor_sync(gmask, dsum, o, 8);
+                    const double mean_d = dsum / (double)BS;
+                    double m2 = 0.0;
+#pragma unroll
+                    for (int j = 0; j < EPT; ++j) {
+                        const double d = (double)f[j] - mean_d;
+                        m2 = fma(d, d, m2);
+                    }
+#pragma unroll
+                    for (int o = 1; o < 8; o <<= 1) m2 += __shfl_xor_sync(gmask, m2, o, 8);
+                    std_h = f2h_bits(__double2float_rn(sqrt(m2 / (double)(BS - 1))));
+                }
+                const float den_f = h2f_bits(f2h_bits(__fadd_rn(h2f_bits(std_h), eps_f)));
+                const float rden = __frcp_rn(den_f);
+                // z test, outlier mask, absmax of the rest
+                unsigned int omask = 0;   // bit j: element j of this thread is an outlier
+                unsigned int maxabs = 0;  // fp32 bits of the largest |x| kept (bit patterns order like the values)
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) {
+                    const float d = h2f_bits(f2h_bits(__fsub_rn(f[j], mean_f)));
+                    const float a = fabsf(d) * rden;
+                    bool is_out = a > fc.t_hi;
+                    if (!is_out && a >= fc.t_lo) {   // inside the guard band: the exact rounded quotient decides
+                        const float z = h2f_bits(f2h_bits(__fdiv_rn(d, den_f)));
+                        is_out = fabsf(z) > fc.thr_f;
+                    }
+                    if (is_out) omask |= 1u << j;
+                    else maxabs = max(maxabs, __float_as_uint(f[j]) & 0x7fffffffu);
+                }
+                int cnt = __popc(omask);
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) {
+                    cnt += __shfl_xor_sync(gmask, cnt, o, 8);
+                    maxabs = max(maxabs, __shfl_xor_sync(gmask, maxabs, o, 8));
+                }
+                uint16_t sc = 0x3c00u;  // 1.0 when the block has no non-outliers
+                if (cnt < BS) {
+                    sc = f2h_bits(__fdiv_rn(__uint_as_float(maxabs), 127.0f));
+                    if (h2f_bits(sc) < eps_f) sc = eps_h;
+                }
+                if (l == 0) s_scale[b] = sc;
+                const float sc_f = h2f_bits(sc);
+                const float rsc = __frcp_rn(sc_f);
+                uint8_t *db = s_dense + b * DSTRIDE + l;
+#pragma unroll
+                for (int j = 0; j < EPT; ++j) {
+                    const float v = f[j] * rsc;
+                    uint16_t qh = f2h_bits(v * (1.f - 2.4e-7f));
+                    if (qh != f2h_bits(v * (1.f + 2.4e-7f))) qh = f2h_bits(__fdiv_rn(f[j], sc_f));  // near a rounding boundary
+                    float r = rintf(h2f_bits(qh));
+                    r = fminf(fmaxf(r, -127.0f), 127.0f);
+                    db[j * 8] = (uint8_t)(int)r;
+                }
+                if (omask) {
+#pragma unroll
+                    for (int j = 0; j < EPT; ++j)
+                        if ((omask >> j) & 1u) {
+                            const int pos = b * BS + j * 8 + l;
+                            atomicOr(&s_mask[pos >> 5], 1u << (pos & 31));
+                        }
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- exclusive scan of outliers per mask word --------------------------------
+        {
+            const uint32_t c = __popc(s_mask[tid]);  // QT_WORDS == QT_THREADS
+            uint32_t inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += n;
+            }
+            if (lane == 31) s_warp_tot[warp] = inc;
+            __syncthreads();
+            uint32_t wbase = 0;
+            for (int w = 0; w < warp; ++w) wbase += s_warp_tot[w];
+            s_wordpre[tid] = wbase + inc - c;
+            if (tid == QT_THREADS - 1) s_tile_total = (int)(wbase + inc);
+        }
+        __syncthreads();
+
+        // ---- decoupled look-back over tiles (warp 0) -------------------------------------
+        if (warp == 0) {
+            const unsigned long long agg = (unsigned long long)s_tile_total;
+            long long prefix = 0;
+            if (tile == 0) {
+                if (lane == 0) st_release_u64(p.status, ST_PREFIX | agg);
+            } else {
+                if (lane == 0) st_release_u64(p.status + tile, ST_AGG | agg);
+                int64_t look = tile - 1;
+                bool done = false;
+                while (!done) {
+                    const int64_t idx = look - lane;
+                    unsigned long long v = ST_PREFIX;  // tiles before the first count as prefix 0
+                    int spins = 0;
+                    bool gave_up = false;
+                    for (;;) {
+                        if (idx >= 0) v = ld_acquire_u64(p.status + idx);
+                        const bool ready = (v >> 62) != 0;
+                        if (__all_sync(0xffffffffu, ready)) break;
+                        if (++spins > QT_SPIN_LIMIT) { gave_up = true; break; }
+                        __nanosleep(64);
+                    }
+                    if (gave_up) {  // record and leave; the host reports ATLAS_ERR_TIMEOUT
+                        if (lane == 0) atomicExch((unsigned long long *)&p.counts[2], 1ull);
+                        break;
+                    }
+                    const unsigned pm = __ballot_sync(0xffffffffu, (v >> 62) == 2);
+                    const int first = pm ? (__ffs(pm) - 1) : 32;
+                    long long contrib = (lane <= first) ? (long long)(v & ST_VALUE) : 0;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
+                    prefix += contrib;
+                    if (pm) done = true; else look -= 32;
+                }
+                if (lane == 0) st_release_u64(p.status + tile, ST_PREFIX | (unsigned long long)(prefix + (long long)agg));
+            }
+            if (lane == 0) {
+                s_tile_prefix = prefix;
+                if (tile == p.num_tiles - 1) {
+                    const long long total_out = prefix + (long long)agg;
+                    p.counts[0] = p.padded - total_out;
+                    p.counts[1] = total_out;
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- phase B: compact the codes in shared memory, outliers straight out --------
+        const long long tile_prefix = s_tile_prefix;
+        const int64_t code_base = tile_base - tile_prefix;  // where this tile's codes start
+        const int shift = p.out_aligned ? (int)(code_base & 15) : 0;
+        for (int i = tid * 4; i < tile_elems; i += QT_THREADS * 4) {
+            const uint32_t word = s_mask[i >> 5];
+            const uint32_t m4 = (word >> (i & 31)) & 0xfu;
+            int before = (int)s_wordpre[i >> 5] + __popc(word & ((1u << (i & 31)) - 1u));
+            const uint32_t c4 = *reinterpret_cast<const uint32_t *>(s_dense + (i / BS) * DSTRIDE + (i % BS));
+            const int dst = shift + i - before;
+            if (m4 == 0u && (dst & 3) == 0) {
+                *reinterpret_cast<uint32_t *>(s_codes + dst) = c4;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if ((m4 >> e) & 1u) {
+                        const long long pos = tile_prefix + before;
+                        if (pos < p.ocap) {
+                            p.ovals[pos] = xref(i + e);
+                            p.oidx[pos] = tile_base + i + e;
+                        }
+                        before++;
+                    } else {
+                        s_codes[shift + i + e - before] = (uint8_t)(c4 >> (8 * e));
+                    }
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- copy the compacted codes out: 16-byte stores inside, bytes at the ragged ends --
+        {
+            const int total = tile_elems - s_tile_total;  // code bytes of this tile
+            const int end = shift + total;
+            int8_t *gdst = p.codes + (code_base - shift);  // 16-byte aligned when out_aligned
+            const int nchunks = (end + 15) >> 4;
+            for (int c = tid; c < nchunks; c += QT_THREADS) {
+                const int lo = c << 4;
+                if (p.out_aligned && lo >= shift && lo + 16 <= end) {
+                    *reinterpret_cast<uint4 *>(gdst + lo) = *reinterpret_cast<const uint4 *>(s_codes + lo);
+                } else {
+                    const int a = max(lo, shift), z = min(lo + 16, end);
+                    for (int q = a; q < z; ++q) gdst[q] = (int8_t)s_codes[q];
+                }
+            }
+            const int64_t block0 = tile_base / BS;
+            for (int b = tid; b < tile_blocks; b += QT_THREADS) p.scales[block0 + b] = s_scale[b];
+        }
+    }
+}
+
+// |fp16(q)| > thr_h  <=>  |q| beyond T, the midpoint between thr_h and the next fp16 number above it
+// (a tie goes to the even neighbour).  Returns T; the kernel uses the exact quotient inside a guard band.
+FastConsts make_fast_consts(uint16_t thr_h) {
+    FastConsts fc;
+    const float thr = __half2float(__ushort_as_half(thr_h));
+    fc.thr_f = thr;
+    float T;
+    if ((thr_h & 0x7fffu) > 0x7c00u) T = INFINITY;            // NaN threshold: nothing compares greater
+    else if (thr_h == 0x7c00u) T = INFINITY;                   // +inf
+    else if (thr_h & 0x8000u) T = -1.f;                        // negative threshold: every |z| is greater
+    else if (thr_h == 0x7bffu) T = 65520.f;                    // next above the largest finite is inf
+    else T = 0.5f * (thr + __half2float(__ushort_as_half((uint16_t)(thr_h + 1))));
+    if (T == INFINITY) { fc.t_lo = INFINITY; fc.t_hi = INFINITY; }
+    else if (T < 0.f) { fc.t_lo = -2.f; fc.t_hi = -1.f; }
+    else { fc.t_lo = T * (1.f - 4.8e-7f); fc.t_hi = T * (1.f + 4.8e-7f); }
+    return fc;
+}
+
 struct DeviceInfo {
     int dev = -1;
     int sms = 0;
@@ -411,8 +729,20 @@ int atlas_quantize(const void *w, int64_t numel, int block_size, double z_thresh
     DeviceInfo di;
     rc = device_info(di);
     if (rc) return rc;
-    const int64_t max_ctas = (int64_t)di.sms * di.quant_ctas_per_sm;
+    const bool fast = block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256;
+    const int per_sm = fast ? (block_size == 256 ? 2 : 4) : di.quant_ctas_per_sm;   // resident CTAs of the fast kernels
+    const int64_t max_ctas = (int64_t)di.sms * per_sm;
     const int grid = (int)(p.num_tiles < max_ctas ? p.num_tiles : max_ctas);
+    if (fast) {
+        const FastConsts fc = make_fast_consts(p.thr_h);
+        switch (block_size) {
+            case 32: quantize_fast_kernel<4><<<grid, QT_THREADS, 0, st>>>(p, fc); break;
+            case 64: quantize_fast_kernel<8><<<grid, QT_THREADS, 0, st>>>(p, fc); break;
+            case 128: quantize_fast_kernel<16><<<grid, QT_THREADS, 0, st>>>(p, fc); break;
+            default: quantize_fast_kernel<32><<<grid, QT_THREADS, 0, st>>>(p, fc); break;
+        }
+        return check_cuda(cudaGetLastError(), "quantize_fast_kernel launch");
+    }
     quantize_kernel<<<grid, QT_THREADS, 0, st>>>(p);
     return check_cuda(cudaGetLastError(), "quantize_kernel launch");
 }
