@@ -7,20 +7,28 @@
 // tile by tile in shared memory and consumed at once by the 5th-generation
 // tensor cores, so it never exists in global memory.
 //
-// One CTA computes a 128 (output features) x 256 (tokens) tile with three rings in shared memory:
-// codes (8 slots of 8 KB: they come from HBM and need the deepest prefetch), activations (3 slots
-// of 32 KB, L2-resident) and rebuilt fp16 weights (3 slots of 16 KB, same index as the activations).
-//   warp 0      activation producer: per 64-wide K step a 2-D TMA load of the 256 x 64 fp16
+// One CTA computes a 128 (output features) x BN (tokens) tile.  The rebuilt fp16 weights never touch
+// shared memory: the dequantizer warps write them straight into tensor memory and the MMA takes its A
+// operand from there, so shared memory only carries what comes from global memory (the kernel is bound
+// by the shared-memory data pipe, not by the tensor pipe).  Rings: codes (8 slots of 8 KB + 256 B of
+// scales: they come from HBM and need the deepest prefetch), activations (4 slots of BN x 64 fp16,
+// L2-resident), rebuilt weights (4 stages of 32 TMEM columns beside the accumulator).
+//   warp 0      activation producer: per 64-wide K step a 2-D TMA load of the BN x 64 fp16
 //               activation tile (128-byte swizzle) completing on `full_x`
 //   warp 2      code producer: a 1-D bulk copy of the step's 8 KB code tile (contiguous in the
 //               tile-major layout) and of the 256 B of scales of its block, completing on `full_c`
-//   warps 3-10  dequantizers (one 16-row strip each): codes -> fp16 A-operand tile in the canonical
-//               K-major 128-byte-swizzled layout, outliers of the tile written over their
-//               (zero-coded) slots from the strip-sorted side-table, then fence.proxy.async +
-//               arrive on `a_ready`; the code slot is released on `empty_c`
-//   warp 1      one thread issues tcgen05.mma (M=128, N=256, K=16, fp16 in, fp32 accumulate in
-//               TMEM) four times per step and commits the slot's `mma_done` mbarrier (which frees
-//               both the activation and the weight slot); after the last step it commits `acc_full`
+//   warps 3-18  dequantizers.  A warp can only reach the TMEM lanes 32 * (warp % 4) .. + 31, and TMEM
+//               lane = tile row for the MMA, so thread = row: warp (q, ph) rebuilds rows 32q .. 32q+31
+//               of every fourth K step (it % 4 == ph, always into A stage ph): four 16-byte code loads
+//               per thread (chunk order rotated per lane so that a quarter-warp covers all banks, then
+//               rotated back with selects), codes -> fp16(fp16(code) * scale), the outliers of the
+//               warp's two strips written over their (zero-coded) slots in registers (side-table
+//               prefetched one step ahead), one tcgen05.st of 32 columns, arrive on `a_ready`; the
+//               code slot is released on `empty_c` as soon as it is in registers
+//   warp 1      one thread issues tcgen05.mma (M=128, N=BN, K=16, A from TMEM, B from shared memory,
+//               fp32 accumulate in TMEM) four times per step and commits the slot's `mma_done`
+//               mbarrier (which frees both the activation slot and the A stage); after the last step
+//               it commits `acc_full`
 //   warps 3-10  epilogue: tcgen05.ld of their TMEM lane quarter (two warps per quarter, half of
 //               the columns each), + bias, convert, transpose through shared memory, 16-byte stores
 // Every mbarrier wait is bounded; if one runs out the CTA sets the caller's status word,
@@ -36,30 +44,33 @@
 namespace atlas {
 namespace {
 
-constexpr int GM_DQ_WARPS = 8;                       // dequantizer / epilogue warps (one 16-row strip each)
+constexpr int GM_DQ_WARPS = 16;                      // dequantizer warps: 4 TMEM lane quarters x 4 K-step phases
+constexpr int GM_EPI_WARPS = 8;                      // the first eight of them drain the accumulator
 constexpr int GM_CTRL_WARPS = 3;                     // activation producer, MMA issuer, code producer
-constexpr int GM_DQ_GROUPS = 2;                      // groups of dequantizer warps taking K steps in turn
-constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_GROUPS * GM_DQ_WARPS) * 32;
+constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_WARPS) * 32;
 constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
 constexpr int GM_BK = 64;   // K per pipeline step (one 128-byte swizzle row of fp16)
-constexpr int GM_XS = 4;    // activation / weight-tile ring depth
-constexpr int GM_CS = 4;    // code ring depth
-constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2;  // 16 KB fp16 weight tile
+constexpr int GM_XS = 4;    // activation ring depth = A stages in tensor memory = K-step phases of the dequantizers
+constexpr int GM_CS = 8;    // code ring depth
+constexpr int GM_A_COLS = GM_BK / 2;             // TMEM columns of one A stage: two fp16 per 32-bit cell
 constexpr uint32_t C_BYTES = GM_BM * GM_BK;      // 8 KB code tile
 constexpr uint32_t S_BYTES = 256;                // one scale block: 128 rows x fp16
+static_assert(GM_XS == 4, "a dequantizer warp owns the A stage of its phase");
 // shared-memory map for a tile of BN tokens (BN = 32, 64, 128 or 256 = UMMA N)
 template <int BN>
 struct Smem {
     static constexpr uint32_t B_BYTES = BN * GM_BK * 2;   // fp16 activation tile
-    static constexpr uint32_t OFF_A = 0;
-    static constexpr uint32_t OFF_B = GM_XS * A_BYTES;
+    static constexpr uint32_t OFF_B = 0;
     static constexpr uint32_t OFF_C = OFF_B + GM_XS * B_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_C + GM_CS * C_BYTES;
     static constexpr uint32_t OFF_S = OFF_BAR + 256;
     static constexpr uint32_t TOTAL = OFF_S + GM_CS * S_BYTES + 1024 /*alignment slack*/;
-    static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    // accumulator columns [0, BN), A stages [BN, BN + 4 * 32); allocations are powers of two
+    static constexpr uint32_t TMEM_COLS = BN + GM_XS * GM_A_COLS <= 256 ? 256 : 512;
+    // the epilogue stages the output tile over the (then idle) activation and code rings
+    static_assert((BN * (GM_BM + 4)) * 4 <= GM_XS * B_BYTES + GM_CS * C_BYTES, "epilogue staging does not fit");
 };
-constexpr int GM_SPIN_LIMIT = 1 << 20;
+constexpr int GM_SPIN_LIMIT = 1 << 20;       // polls per wait
 
 // ---- PTX wrappers ----------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -82,11 +93,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within the spin limit.
+// Bounded wait: false if the phase did not complete within the poll limit.  NS > 0 sleeps between polls, which
+// keeps a waiting warp out of the issue slots of the warps that work on the same scheduler.
+template <int NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < GM_SPIN_LIMIT; ++i)
+    for (int i = 0; i < GM_SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (NS > 0) __nanosleep(NS);
+    }
     return false;
+}
+// Same, agreed on by the whole (converged) warp, so that warp-wide instructions after it stay warp-wide.
+template <int NS = 0>
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const volatile int *abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait<NS>(bar, parity) && !*abort_flag) != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
@@ -104,12 +124,13 @@ __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.f
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 lanes x 8 columns (16 fp16 along K, two per cell)
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -126,6 +147,19 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 32 lanes (this warp's quarter) x 32 columns: thread t writes v[0..31] to lane t, columns taddr.col .. + 31
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: K-major operand tile, rows of 128 bytes (64 fp16), 128-byte
 // swizzle, 8-row groups 1024 bytes apart.  Fields: start address >> 4 at bit 0, leading byte
@@ -180,11 +214,11 @@ struct GemmParams {
 
 template <int BN>
 __global__ void __launch_bounds__(GM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap c_map, GemmParams p) {
     using SM = Smem<BN>;
     // the next kernel of the stream may start its own weight-only prologue right away
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    constexpr uint32_t B_BYTES = SM::B_BYTES, OFF_A = SM::OFF_A, OFF_B = SM::OFF_B, OFF_C = SM::OFF_C, OFF_BAR = SM::OFF_BAR,
+    constexpr uint32_t B_BYTES = SM::B_BYTES, OFF_B = SM::OFF_B, OFF_C = SM::OFF_C, OFF_BAR = SM::OFF_BAR,
                        OFF_S = SM::OFF_S, TMEM_COLS = SM::TMEM_COLS;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -210,12 +244,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     if (tid == 0) {
         for (int s = 0; s < GM_XS; ++s) {
             mbar_init(full_x(s), 1);
-            mbar_init(aready_bar(s), GM_DQ_WARPS * 32);
+            mbar_init(aready_bar(s), 4 * 32);   // the four warps (one per TMEM lane quarter) of the stage's phase
             mbar_init(mma_done(s), 1);
         }
         for (int s = 0; s < GM_CS; ++s) {
             mbar_init(full_c(s), 1);
-            mbar_init(empty_c(s), GM_DQ_WARPS);
+            mbar_init(empty_c(s), 4);
         }
         mbar_init(accfull_bar, 1);
         *s_abort = 0;
@@ -238,7 +272,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int it = 0; it < KT; ++it) {
                 const int s = it % GM_XS, round = it / GM_XS;
-                if (round > 0 && !mbar_wait(mma_done(s), (round - 1) & 1)) { *s_abort = 1; break; }
+                if (round > 0 && !mbar_wait<200>(mma_done(s), (round - 1) & 1)) { *s_abort = 1; break; }
                 if (*s_abort) break;
                 mbar_arrive_expect_tx(full_x(s), B_BYTES);
                 tma_load_2d(base + OFF_B + s * B_BYTES, &x_map, (kt_begin + it) * GM_BK, m0, full_x(s));
@@ -247,14 +281,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
     } else if (warp == 2) {
         // ------------------------------ code producer ------------------------------
         if (lane == 0) {
-            const uint8_t *ctile = p.tiles + ((size_t)blockIdx.x * p.k_tiles + kt_begin) * C_BYTES;
+            const int64_t crow0 = (int64_t)blockIdx.x * p.k_tiles + kt_begin;   // code tiles are rows of 128 in the map
             const int bpr = p.n_cols / p.bs;
             for (int it = 0; it < KT; ++it) {
                 const int s = it % GM_CS, round = it / GM_CS;
-                if (round > 0 && !mbar_wait(empty_c(s), (round - 1) & 1)) { *s_abort = 1; break; }
+                if (round > 0 && !mbar_wait<200>(empty_c(s), (round - 1) & 1)) { *s_abort = 1; break; }
                 if (*s_abort) break;
                 mbar_arrive_expect_tx(full_c(s), C_BYTES + (p.bs_tiles ? S_BYTES : 0));
-                bulk_load_1d(base + OFF_C + s * C_BYTES, ctile + (size_t)it * C_BYTES, C_BYTES, full_c(s));
+                // the 8 KB code tile is a 128-row x 64-byte matrix; the 64-byte swizzle spreads a column of 16-byte
+                // chunks over all banks for the dequantizers (thread = row)
+                tma_load_2d(base + OFF_C + s * C_BYTES, &c_map, 0, (int)((crow0 + it) * GM_BM), full_c(s));
                 if (p.bs_tiles)
                     bulk_load_1d(base + OFF_S + s * S_BYTES,
                                  p.scales_t + ((size_t)blockIdx.x * bpr + (kt_begin + it) / p.bs_tiles) * 128, S_BYTES, full_c(s));
@@ -266,13 +302,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
             bool ok = true;
             for (int it = 0; it < KT && ok; ++it) {
                 const int s = it % GM_XS, round = it / GM_XS;
-                ok = mbar_wait(aready_bar(s), round & 1) && mbar_wait(full_x(s), round & 1) && !*s_abort;
+                ok = mbar_wait<20>(aready_bar(s), round & 1) && mbar_wait<20>(full_x(s), round & 1) && !*s_abort;
                 if (!ok) break;
                 tcgen05_fence_after();
-                const uint64_t da = make_smem_desc(base + OFF_A + s * A_BYTES), db = make_smem_desc(base + OFF_B + s * B_BYTES);
+                const uint64_t db = make_smem_desc(base + OFF_B + s * B_BYTES);
+                const uint32_t ta = tmem_base + (uint32_t)BN + (uint32_t)(s * GM_A_COLS);
 #pragma unroll
-                for (int k = 0; k < GM_BK / 16; ++k)  // 32 bytes (16 fp16) further along K per step
-                    umma_f16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), gm_idesc<BN>(), (it | k) != 0);
+                for (int k = 0; k < GM_BK / 16; ++k)  // 16 fp16 further along K per step: 8 TMEM columns, 32 bytes of the B tile
+                    umma_f16_ts(tmem_base, ta + (uint32_t)(k * 8), db + (uint64_t)(k * 2), gm_idesc<BN>(), (it | k) != 0);
                 umma_commit(mma_done(s));  // arrives when these MMAs have finished reading both slots
             }
             if (!ok) *s_abort = 1;
@@ -280,92 +317,131 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
         }
     } else {
         // ------------------------------ dequantizers, then epilogue ------------------------------
-        const int dw = (warp - GM_CTRL_WARPS) % GM_DQ_WARPS;   // 0..7: strip dw of the 128-row tile
-        const int grp = (warp - GM_CTRL_WARPS) / GM_DQ_WARPS;  // this group rebuilds the steps it == grp (mod groups)
-        const int g = lane >> 2, tig = lane & 3;
+        const int dwi = warp - GM_CTRL_WARPS;     // 0..15
+        const int q = warp & 3;                   // TMEM lane quarter this warp may access: rows 32q .. 32q+31 of the tile
+        const int ph = dwi >> 2;                  // this warp rebuilds the K steps it == ph (mod 4), always into A stage ph
+        const int rl = q * 32 + lane;             // row of the tile (= TMEM lane) this thread rebuilds
+        const int rs = lane & 15;                 // its row inside the 16-row strip
+        const int swz = (lane >> 1) & 3;          // 64-byte swizzle of this row's 16-byte chunks
         const int bpr = p.n_cols / p.bs;
         const uint16_t *sc_tile = p.scales_t + (int64_t)blockIdx.x * bpr * 128;
-        const int r0 = dw * 16 + g, r1 = r0 + 8;   // the two rows of the tile this thread rebuilds in every K step
-        // outlier cursor of the strip (its list is sorted by column)
-        const int64_t strip = (int64_t)blockIdx.x * 8 + dw;
-        int cur = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + kt_begin);
-        const int end = __ldg(p.chunk_ptr + strip * (p.n_chunks + 1) + kt_begin + KT);
-        // the warp keeps the next 32 entries of the list in registers, one per lane
-        uint32_t buf_ent = cur + lane < end ? __ldg(p.entries + cur + lane) : 0x00ffffffu;
-        uint32_t buf_val = cur + lane < end ? (uint32_t)__ldg(p.ovals + cur + lane) : 0u;
-        const uint32_t sw0 = (uint32_t)((2 * tig) ^ g) << 4, sw1 = (uint32_t)((2 * tig + 1) ^ g) << 4;  // swizzled 16-byte chunks
+        // outlier lists (sorted by column) of the warp's two strips: lanes 0-15 serve strip 2q, lanes 16-31 strip 2q+1
+        const int64_t strip = (int64_t)blockIdx.x * 8 + 2 * q + (lane >> 4);
+        const int32_t *cp = p.chunk_ptr + strip * (p.n_chunks + 1) + kt_begin;
+        const int ej = lane & 15;                 // which entry of its strip's list this lane buffers
+        const uint32_t code_off = (uint32_t)rl * 64u;   // the tile is a 128 x 64-byte row-major matrix
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)BN + (uint32_t)(ph * GM_A_COLS);
+        // side-table pipeline: [b0, e0) + the buffered entries belong to the warp's current step, [b1, e1) to its next.
+        // A buffered entry is packed for the patch loop: owner lane (strip half * 16 + row) << 22 | column inside the
+        // K step << 16 | fp16 value; 63 in the lane field matches nobody.
+        auto pack = [&](uint32_t ent, uint32_t val) -> uint32_t {
+            return ((uint32_t)(lane & 16) | (ent >> 24)) << 22 | (ent & 63u) << 16 | val;
+        };
+        constexpr uint32_t NO_ENTRY = 63u << 22;
+        int b0 = 0, e0 = 0, b1 = 0, e1 = 0;
+        uint32_t pk0 = NO_ENTRY;
+        if (ph < KT) {
+            b0 = __ldg(cp + ph);
+            e0 = __ldg(cp + ph + 1);
+            if (b0 + ej < e0) pk0 = pack(__ldg(p.entries + b0 + ej), __ldg(p.ovals + b0 + ej));
+        }
+        if (ph + 4 < KT) { b1 = __ldg(cp + ph + 4); e1 = __ldg(cp + ph + 5); }
         bool ok = true;
-        for (int it = grp; it < KT && ok; it += GM_DQ_GROUPS) {
+        for (int it = ph; it < KT && ok; it += 4) {
+            // prefetch: the entries of the next step (their range arrived a step ago) and the range of the one after
+            uint32_t ent1 = 0, val1 = 0;
+            const bool has1 = b1 + ej < e1;
+            if (has1) { ent1 = __ldg(p.entries + b1 + ej); val1 = __ldg(p.ovals + b1 + ej); }
+            int b2 = 0, e2 = 0;
+            if (it + 8 < KT) { b2 = __ldg(cp + it + 8); e2 = __ldg(cp + it + 9); }
+
             const int sc_ = it % GM_CS, cround = it / GM_CS;   // code slot
-            const int sa = it % GM_XS, around = it / GM_XS;    // weight-tile slot
-            if (!mbar_wait(full_c(sc_), cround & 1) || *s_abort) { ok = false; break; }
-            const unsigned char *codes = base_ptr + OFF_C + sc_ * C_BYTES + (dw * 2 * 32 + lane) * 16;
+            const int around = it / GM_XS;                     // use count of A stage ph
+            if (!mbar_wait_warp<40>(full_c(sc_), cround & 1, s_abort)) { ok = false; break; }
+            const unsigned char *codes = base_ptr + OFF_C + sc_ * C_BYTES + code_off;
             const int k0 = (kt_begin + it) * GM_BK;
-            const uint4 c0 = *reinterpret_cast<const uint4 *>(codes);          // row r0, k 16*tig .. +15
-            const uint4 c1 = *reinterpret_cast<const uint4 *>(codes + 512);    // row r1
-            __half sh0, sh1;
+            // the row's 64 codes: chunk c sits at c ^ ((row >> 1) & 3) under the 64-byte swizzle, so the 8 lanes of a
+            // quarter-warp (rows 64 bytes apart) cover all 32 banks
+            uint4 L[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) L[c] = *reinterpret_cast<const uint4 *>(codes + ((c ^ swz) << 4));
+            __half sh[4];
             if (p.bs_tiles) {
                 const uint16_t *scs = reinterpret_cast<const uint16_t *>(base_ptr + OFF_S + sc_ * S_BYTES);
-                sh0 = __ushort_as_half(scs[r0]);
-                sh1 = __ushort_as_half(scs[r1]);
+                sh[0] = sh[1] = sh[2] = sh[3] = __ushort_as_half(scs[rl]);
             } else {
-                const int kb = (k0 + tig * 16) / p.bs;
-                sh0 = __ushort_as_half(__ldg(sc_tile + (int64_t)kb * 128 + r0));
-                sh1 = __ushort_as_half(__ldg(sc_tile + (int64_t)kb * 128 + r1));
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    sh[c] = __ushort_as_half(__ldg(sc_tile + (int64_t)((k0 + c * 16) / p.bs) * 128 + rl));
             }
-            const __half2 s02 = __half2half2(sh0), s12 = __half2half2(sh1);
-            uint4 o0, o1, o2, o3;
-            dequant4(c0.x, s02, o0.x, o0.y);
-            dequant4(c0.y, s02, o0.z, o0.w);
-            dequant4(c0.z, s02, o1.x, o1.y);
-            dequant4(c0.w, s02, o1.z, o1.w);
-            dequant4(c1.x, s12, o2.x, o2.y);
-            dequant4(c1.y, s12, o2.z, o2.w);
-            dequant4(c1.z, s12, o3.x, o3.y);
-            dequant4(c1.w, s12, o3.z, o3.w);
             // the code slot is in registers: hand it back (one arrival per warp)
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_c(sc_));
-            // the weight-tile slot must have been read by the MMAs of its previous use
-            if (around > 0 && !mbar_wait(mma_done(sa), (around - 1) & 1)) { ok = false; break; }
-            unsigned char *stp = base_ptr + OFF_A + sa * A_BYTES;
-            unsigned char *row0 = stp + (r0 >> 3) * 1024 + g * 128;   // r0 & 7 == r1 & 7 == g
-            unsigned char *row1 = row0 + 1024;
-            *reinterpret_cast<uint4 *>(row0 + sw0) = o0;   // k 16*tig .. +7
-            *reinterpret_cast<uint4 *>(row0 + sw1) = o1;   // k 16*tig+8 .. +15
-            *reinterpret_cast<uint4 *>(row1 + sw0) = o2;
-            *reinterpret_cast<uint4 *>(row1 + sw1) = o3;
-            // outliers of the strip inside this K step: every lane looks at its own buffered entry and
-            // writes the raw fp16 value over the zero-coded slot (after the warp's stores above)
-            __syncwarp();
-            for (;;) {
-                const int kk = (int)(buf_ent & 0xffffffu) - k0;   // < 0: belongs to a step of another group
-                const bool in = kk < GM_BK;
-                const bool mine = in && kk >= 0;
-                if (mine) {
-                    const int rs = (int)(buf_ent >> 24);
-                    unsigned char *rowp = stp + (dw * 2 + (rs >> 3)) * 1024 + (rs & 7) * 128;
-                    *reinterpret_cast<uint16_t *>(rowp + (((kk >> 3) ^ (rs & 7)) << 4) + (kk & 7) * 2) = (uint16_t)buf_val;
-                }
-                const int n_in = __popc(__ballot_sync(0xffffffffu, in));
-                if (n_in == 0) break;
-                cur += n_in;                                      // consumed: refill the buffer from there
-                buf_ent = cur + lane < end ? __ldg(p.entries + cur + lane) : 0x00ffffffu;
-                buf_val = cur + lane < end ? (uint32_t)__ldg(p.ovals + cur + lane) : 0u;
-                if (n_in < 32) break;                             // the run of this step ended inside the buffer
+            uint32_t o[32];   // the row's 64 fp16 weights of this K step, two per register
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const __half2 s2 = __half2half2(sh[c]);
+                dequant4(L[c].x, s2, o[c * 8 + 0], o[c * 8 + 1]);
+                dequant4(L[c].y, s2, o[c * 8 + 2], o[c * 8 + 3]);
+                dequant4(L[c].z, s2, o[c * 8 + 4], o[c * 8 + 5]);
+                dequant4(L[c].w, s2, o[c * 8 + 6], o[c * 8 + 7]);
             }
-            fence_async_smem();  // make the generic-proxy writes visible to the tensor core's reads
-            mbar_arrive(aready_bar(sa));
+            // outliers of the two strips inside this K step.  Every lane finds the buffered entries of its own row
+            // (five ballots over the owner field), pulls them with one shuffle per round and puts the raw fp16 value
+            // over the zero-coded slot; the rounds are the largest number of outliers any row has in this step.
+            auto put = [&](uint32_t pk, bool have) {
+                const uint32_t onehot = have ? 1u << ((pk >> 17) & 31u) : 0u;      // which of the row's 32 registers
+                const uint32_t sel = (pk & 0x10000u) ? 0x5410u : 0x3254u;          // odd column: high half, even: low half
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (onehot & (1u << i)) o[i] = __byte_perm(o[i], pk, sel);
+            };
+            {
+                const uint32_t own = pk0 >> 22;   // owner lane of the entry this lane buffers, 63: none
+                uint32_t mine = __ballot_sync(0xffffffffu, own != 63u);
+#pragma unroll
+                for (int bit = 0; bit < 5; ++bit) {
+                    const uint32_t bb = __ballot_sync(0xffffffffu, (own >> bit) & 1u);
+                    mine &= ((lane >> bit) & 1) ? bb : ~bb;
+                }
+                const int rounds = __reduce_max_sync(0xffffffffu, __popc(mine));
+                for (int r = 0; r < rounds; ++r) {
+                    const bool have = mine != 0;
+                    const uint32_t pk = __shfl_sync(0xffffffffu, pk0, have ? __ffs(mine) - 1 : 0);
+                    mine &= mine - 1;
+                    put(pk, have);
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {   // rare: more than 16 outliers of one strip inside one K step
+                const int cnt = __shfl_sync(0xffffffffu, e0 - b0, h * 16);
+                if (cnt > 16) {
+                    const int bb = __shfl_sync(0xffffffffu, b0, h * 16);
+                    for (int j = 16; j < cnt; ++j) {
+                        const uint32_t ent = __ldg(p.entries + bb + j);
+                        const uint32_t pk = ((uint32_t)(h * 16) | (ent >> 24)) << 22 | (ent & 63u) << 16 | (uint32_t)__ldg(p.ovals + bb + j);
+                        put(pk, (pk >> 22) == (uint32_t)lane);
+                    }
+                }
+            }
+            // the A stage must have been read by the MMAs of its previous use
+            if (around > 0 && !mbar_wait_warp<100>(mma_done(ph), (around - 1) & 1, s_abort)) { ok = false; break; }
+            tcgen05_fence_after();
+            tmem_st_32x32b_x32(taddr, o);
+            tmem_st_wait();
+            tcgen05_fence_before();
+            mbar_arrive(aready_bar(ph));
+            pk0 = has1 ? pack(ent1, val1) : NO_ENTRY;
+            b0 = b1; e0 = e1; b1 = b2; e1 = e2;
         }
         if (!ok) *s_abort = 1;
 
         // epilogue: TMEM lane = output feature, column = token.  The accumulators go through shared
         // memory (the rings are idle by now) so that y is written in 16-byte pieces along a token row.
-        if (grp != 0) {
-            // only the first group drains the accumulators
-        } else if (mbar_wait(accfull_bar, 0) && !*s_abort) {
+        if (dwi >= GM_EPI_WARPS) {
+            // only the first eight dequantizer warps drain the accumulator
+        } else if (mbar_wait_warp<200>(accfull_bar, 0, s_abort)) {
             tcgen05_fence_after();
-            const int q = warp & 3;                         // the TMEM lane quarter this warp may read
             const int half = (warp - GM_CTRL_WARPS) >> 2;   // two warps share a quarter: columns [0,128) and [128,256)
             const int nl = q * 32 + lane;                   // feature inside the tile
             const int n = n0 + nl;
@@ -373,7 +449,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
             // staging tile [BN tokens][128 features (+ pad)] in the idle rings: 16-bit outputs, or fp32
             // partial sums when K is split between CTAs
             const bool partial = p.splits > 1;
-            unsigned char *stage = base_ptr + OFF_A;
+            unsigned char *stage = base_ptr + OFF_B;
             const int st_bytes = partial ? (GM_BM + 4) * 4 : (GM_BM + 8) * 2;   // row stride; pads keep banks apart
             for (int c = half; c < BN / 32; c += 2) {
                 if (m0 + c * 32 >= p.m) break;  // warp-uniform: no tokens left in this tile
@@ -393,14 +469,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
                 }
             }
             // all eight epilogue warps have staged their part
-            asm volatile("bar.sync 1, %0;" ::"n"(GM_DQ_WARPS * 32) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(GM_EPI_WARPS * 32) : "memory");
             const int et = tid - GM_CTRL_WARPS * 32;         // 0..255
             const int rows_left = min(BN, p.m - m0);
             if (partial) {
                 // fp32 partial tile -> partials[z][m][n], 16 bytes (4 features) per thread and store
                 float *dst0 = p.partials + (size_t)blockIdx.z * p.m * p.n_rows;
                 const bool vec_ok = (n0 + GM_BM <= p.n_rows) && (p.n_rows % 4 == 0);
-                for (int idx = et; idx < rows_left * (GM_BM / 4); idx += GM_DQ_WARPS * 32) {
+                for (int idx = et; idx < rows_left * (GM_BM / 4); idx += GM_EPI_WARPS * 32) {
                     const int row = idx >> 5, piece = idx & 31;
                     const float *src = reinterpret_cast<const float *>(stage + (size_t)row * st_bytes) + piece * 4;
                     float *dst = dst0 + (size_t)(m0 + row) * p.n_rows + n0 + piece * 4;
@@ -413,7 +489,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, GemmParams p) {
                 }
             } else {
                 const bool vec_ok = (n0 + GM_BM <= p.n_rows) && (p.ldy % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
-                for (int idx = et; idx < rows_left * (GM_BM / 8); idx += GM_DQ_WARPS * 32) {
+                for (int idx = et; idx < rows_left * (GM_BM / 8); idx += GM_EPI_WARPS * 32) {
                     const int row = idx >> 4, piece = idx & 15;  // 16 pieces of 8 features per token row
                     const uint16_t *src = reinterpret_cast<const uint16_t *>(stage + (size_t)row * st_bytes) + piece * 8;
                     uint16_t *dst = reinterpret_cast<uint16_t *>(p.y) + (int64_t)(m0 + row) * p.ldy + n0 + piece * 8;
@@ -546,7 +622,7 @@ int gemm_sm_count() {
 }
 
 template <int BN>
-int launch_gemm(const CUtensorMap &x_map, const GemmParams &p, cudaStream_t st) {
+int launch_gemm(const CUtensorMap &x_map, const CUtensorMap &c_map, const GemmParams &p, cudaStream_t st) {
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -558,7 +634,7 @@ int launch_gemm(const CUtensorMap &x_map, const GemmParams &p, cudaStream_t st) 
     }
     cudaLaunchConfig_t cfg = pdl_config(dim3((unsigned)ceil_div_i64(p.n_rows, GM_BM), (unsigned)ceil_div_i64(p.m, BN), (unsigned)p.splits),
                                         dim3(GM_THREADS), Smem<BN>::TOTAL, st);
-    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_kernel<BN>, x_map, p), "gemm_kernel launch");
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_kernel<BN>, x_map, c_map, p), "gemm_kernel launch");
 }
 
 }  // namespace
@@ -633,6 +709,17 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
                          estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     ATLAS_RETURN_IF(cr != CUDA_SUCCESS, ATLAS_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)cr);
+    // the code tiles as one matrix of 64-byte rows: tile (row tile rt, k-tile kt) = rows (rt * k_tiles + kt) * 128 .. + 127
+    CUtensorMap c_map;
+    {
+        const cuuint64_t cdim[2] = {(cuuint64_t)GM_BK, (cuuint64_t)(ceil_div_i64(n_rows, GM_BM) * (n_cols / GM_BK) * GM_BM)};
+        const cuuint64_t cstride[1] = {(cuuint64_t)GM_BK};
+        const cuuint32_t cbox[2] = {(cuuint32_t)GM_BK, (cuuint32_t)GM_BM};
+        cr = encode(&c_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(tiles), cdim, cstride, cbox, estride,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        ATLAS_RETURN_IF(cr != CUDA_SUCCESS, ATLAS_ERR_LAUNCH, "cuTensorMapEncodeTiled (codes) failed with %d", (int)cr);
+    }
 
     GemmParams p;
     p.tiles = tiles;
@@ -655,10 +742,10 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
     p.partials = (float *)((char *)workspace + GM_WS_HEADER + xcopy);
     p.error_flag = status;
     switch (bn) {
-        case 32: rc = launch_gemm<32>(x_map, p, st); break;
-        case 64: rc = launch_gemm<64>(x_map, p, st); break;
-        case 128: rc = launch_gemm<128>(x_map, p, st); break;
-        default: rc = launch_gemm<256>(x_map, p, st); break;
+        case 32: rc = launch_gemm<32>(x_map, c_map, p, st); break;
+        case 64: rc = launch_gemm<64>(x_map, c_map, p, st); break;
+        case 128: rc = launch_gemm<128>(x_map, c_map, p, st); break;
+        default: rc = launch_gemm<256>(x_map, c_map, p, st); break;
     }
     if (rc) return rc;
     if (p.splits > 1) {
