@@ -14,7 +14,7 @@
 // scales: they come from HBM and need the deepest prefetch), activations (4 slots of BN x 64 fp16,
 // L2-resident), rebuilt weights (4 stages of 32 TMEM columns beside the accumulator).
 //   warp 0      activation producer: per 64-wide K step a 2-D TMA load of the BN x 64 fp16
-//               activation tile (128-byte swizzle) completing on `full_x`
+//               activation tile (128-byte swizzle) completing on the step's `ready` barrier
 //   warp 2      code producer: a 1-D bulk copy of the step's 8 KB code tile (contiguous in the
 //               tile-major layout) and of the 256 B of scales of its block, completing on `full_c`
 //   warps 3-18  dequantizers.  A warp can only reach the TMEM lanes 32 * (warp % 4) .. + 31, and TMEM
@@ -23,7 +23,7 @@
 //               per thread (chunk order rotated per lane so that a quarter-warp covers all banks, then
 //               rotated back with selects), codes -> fp16(fp16(code) * scale), the outliers of the
 //               warp's two strips written over their (zero-coded) slots in registers (side-table
-//               prefetched one step ahead), one tcgen05.st of 32 columns, arrive on `a_ready`; the
+//               prefetched one step ahead), one tcgen05.st of 32 columns, arrive on `ready`; the
 //               code slot is released on `empty_c` as soon as it is in registers
 //   warp 1      one thread issues tcgen05.mma (M=128, N=BN, K=16, A from TMEM, B from shared memory,
 //               fp32 accumulate in TMEM) four times per step and commits the slot's `mma_done`
@@ -225,14 +225,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     const uint32_t base = (raw + 1023u) & ~1023u;          // operand tiles need 1024-byte alignment
     unsigned char *base_ptr = smem_raw + (base - raw);
     const uint32_t bars = base + OFF_BAR;   // mbarriers, 8 bytes each
-    auto full_x = [&](int s) { return bars + 8u * s; };
-    auto aready_bar = [&](int s) { return bars + 8u * (GM_XS + s); };
-    auto mma_done = [&](int s) { return bars + 8u * (2 * GM_XS + s); };
-    auto full_c = [&](int s) { return bars + 8u * (3 * GM_XS + s); };
-    auto empty_c = [&](int s) { return bars + 8u * (3 * GM_XS + GM_CS + s); };
-    const uint32_t accfull_bar = bars + 8u * (3 * GM_XS + 2 * GM_CS);
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + OFF_BAR + 8 * (3 * GM_XS + 2 * GM_CS + 1));
-    volatile int *s_abort = reinterpret_cast<volatile int *>(base_ptr + OFF_BAR + 8 * (3 * GM_XS + 2 * GM_CS + 1) + 8);
+    // ready(s): the activation tile has landed (one arrival + its bytes) and the four dequantizer warps of the
+    // stage have stored the weights (128 arrivals); the MMA thread waits on this one barrier per K step
+    auto ready_bar = [&](int s) { return bars + 8u * s; };
+    auto mma_done = [&](int s) { return bars + 8u * (GM_XS + s); };
+    auto full_c = [&](int s) { return bars + 8u * (2 * GM_XS + s); };
+    auto empty_c = [&](int s) { return bars + 8u * (2 * GM_XS + GM_CS + s); };
+    constexpr int N_BARS = 2 * GM_XS + 2 * GM_CS + 1;
+    static_assert(N_BARS * 8 + 16 <= 256, "barrier area");
+    const uint32_t accfull_bar = bars + 8u * (N_BARS - 1);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + OFF_BAR + 8 * N_BARS);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(base_ptr + OFF_BAR + 8 * N_BARS + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * GM_BM;  // first weight row (output feature) of the tile
@@ -243,8 +246,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
 
     if (tid == 0) {
         for (int s = 0; s < GM_XS; ++s) {
-            mbar_init(full_x(s), 1);
-            mbar_init(aready_bar(s), 4 * 32);   // the four warps (one per TMEM lane quarter) of the stage's phase
+            mbar_init(ready_bar(s), 4 * 32 + 1);
             mbar_init(mma_done(s), 1);
         }
         for (int s = 0; s < GM_CS; ++s) {
@@ -272,10 +274,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int it = 0; it < KT; ++it) {
                 const int s = it % GM_XS, round = it / GM_XS;
-                if (round > 0 && !mbar_wait<200>(mma_done(s), (round - 1) & 1)) { *s_abort = 1; break; }
+                if (round > 0 && !mbar_wait<32>(mma_done(s), (round - 1) & 1)) { *s_abort = 1; break; }
                 if (*s_abort) break;
-                mbar_arrive_expect_tx(full_x(s), B_BYTES);
-                tma_load_2d(base + OFF_B + s * B_BYTES, &x_map, (kt_begin + it) * GM_BK, m0, full_x(s));
+                mbar_arrive_expect_tx(ready_bar(s), B_BYTES);
+                tma_load_2d(base + OFF_B + s * B_BYTES, &x_map, (kt_begin + it) * GM_BK, m0, ready_bar(s));
             }
         }
     } else if (warp == 2) {
@@ -299,18 +301,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            bool ok = true;
-            for (int it = 0; it < KT && ok; ++it) {
-                const int s = it % GM_XS, round = it / GM_XS;
-                ok = mbar_wait<20>(aready_bar(s), round & 1) && mbar_wait<20>(full_x(s), round & 1) && !*s_abort;
-                if (!ok) break;
-                tcgen05_fence_after();
-                const uint64_t db = make_smem_desc(base + OFF_B + s * B_BYTES);
-                const uint32_t ta = tmem_base + (uint32_t)BN + (uint32_t)(s * GM_A_COLS);
+            // One barrier poll, four MMAs and one commit per K step.  An MMA issue, a poll and a commit each cost this
+            // single thread 70-180 cycles; the tensor pipe needs 4 x 128 for the step, so the poll for the next step is
+            // issued between the MMAs of this one (its result is only looked at afterwards) and nothing but the
+            // commit stands between the last MMA of a step and the first of the next.
+            bool ok = KT > 0 && mbar_wait(ready_bar(0), 0);
+            uint64_t db[GM_XS];
 #pragma unroll
-                for (int k = 0; k < GM_BK / 16; ++k)  // 16 fp16 further along K per step: 8 TMEM columns, 32 bytes of the B tile
-                    umma_f16_ts(tmem_base, ta + (uint32_t)(k * 8), db + (uint64_t)(k * 2), gm_idesc<BN>(), (it | k) != 0);
-                umma_commit(mma_done(s));  // arrives when these MMAs have finished reading both slots
+            for (int s = 0; s < GM_XS; ++s) db[s] = make_smem_desc(base + OFF_B + s * B_BYTES);
+            const uint32_t ta0 = tmem_base + (uint32_t)BN;
+            for (int it = 0; it < KT && ok; ++it) {
+                const int s = it % GM_XS;
+                tcgen05_fence_after();
+                const uint64_t dbs = db[s];
+                const uint32_t ta = ta0 + (uint32_t)(s * GM_A_COLS);
+                umma_f16_ts(tmem_base, ta, dbs, gm_idesc<BN>(), it != 0);
+                umma_f16_ts(tmem_base, ta + 8u, dbs + 2u, gm_idesc<BN>(), 1u);
+                // the next step's barrier: one poll now, looked at after the commit
+                const int sn = (it + 1) % GM_XS;
+                const uint32_t pn = ((it + 1) / GM_XS) & 1;
+                const bool next_ready = it + 1 < KT ? mbar_try_wait(ready_bar(sn), pn) : true;
+                umma_f16_ts(tmem_base, ta + 16u, dbs + 4u, gm_idesc<BN>(), 1u);
+                umma_f16_ts(tmem_base, ta + 24u, dbs + 6u, gm_idesc<BN>(), 1u);
+                umma_commit(mma_done(s));  // arrives when these MMAs have finished reading the slot and the A stage
+                if (!next_ready) ok = mbar_wait(ready_bar(sn), pn);
+                if ((it & 15) == 15 && *s_abort) ok = false;
             }
             if (!ok) *s_abort = 1;
             umma_commit(accfull_bar);  // arrives when every MMA issued so far is complete
@@ -331,29 +346,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
         const int ej = lane & 15;                 // which entry of its strip's list this lane buffers
         const uint32_t code_off = (uint32_t)rl * 64u;   // the tile is a 128 x 64-byte row-major matrix
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)BN + (uint32_t)(ph * GM_A_COLS);
-        // side-table pipeline: [b0, e0) + the buffered entries belong to the warp's current step, [b1, e1) to its next.
-        // A buffered entry is packed for the patch loop: owner lane (strip half * 16 + row) << 22 | column inside the
-        // K step << 16 | fp16 value; 63 in the lane field matches nobody.
+        // Side-table pipeline.  The warp's steps are numbered n = 0, 1, .. (K step it = ph + 4 n).  The entry ranges
+        // [cp[it], cp[it + 1]) of 16 consecutive steps sit in one register per lane (lane j of each half-warp: step
+        // 16 * block + j of its strip), two such blocks alternate; the entries of a step are requested two steps
+        // ahead, one per lane, and packed for the patch when the step starts: owner lane (strip half * 16 + row)
+        // << 22 | column inside the K step << 16 | fp16 value; 63 in the lane field matches nobody.
         auto pack = [&](uint32_t ent, uint32_t val) -> uint32_t {
             return ((uint32_t)(lane & 16) | (ent >> 24)) << 22 | (ent & 63u) << 16 | val;
         };
         constexpr uint32_t NO_ENTRY = 63u << 22;
-        int b0 = 0, e0 = 0, b1 = 0, e1 = 0;
-        uint32_t pk0 = NO_ENTRY;
-        if (ph < KT) {
-            b0 = __ldg(cp + ph);
-            e0 = __ldg(cp + ph + 1);
-            if (b0 + ej < e0) pk0 = pack(__ldg(p.entries + b0 + ej), __ldg(p.ovals + b0 + ej));
-        }
-        if (ph + 4 < KT) { b1 = __ldg(cp + ph + 4); e1 = __ldg(cp + ph + 5); }
+        const int nsteps = ph < KT ? (KT - ph + 3) >> 2 : 0;
+        int rbA = 0, reA = 0, rbB = 0, reB = 0;
+        auto load_ranges = [&](int block, int &rb, int &re) {
+            const int nn = block * 16 + ej;
+            rb = 0;
+            re = 0;
+            if (nn < nsteps) { rb = __ldg(cp + ph + 4 * nn); re = __ldg(cp + ph + 4 * nn + 1); }
+        };
+        auto range_of = [&](int nn, int &b_, int &e_) {   // ranges of step nn for both half-warps; (0, 0) past the end
+            const bool odd = (nn >> 4) & 1;
+            const int src = (lane & 16) | (nn & 15);
+            b_ = __shfl_sync(0xffffffffu, odd ? rbB : rbA, src);
+            e_ = __shfl_sync(0xffffffffu, odd ? reB : reA, src);
+        };
+        load_ranges(0, rbA, reA);
+        load_ranges(1, rbB, reB);
+        int b0, e0, b1, e1;
+        uint32_t ent0 = 0, val0 = 0, ent1 = 0, val1 = 0;
+        range_of(0, b0, e0);
+        range_of(1, b1, e1);
+        if (b0 + ej < e0) { ent0 = __ldg(p.entries + b0 + ej); val0 = __ldg(p.ovals + b0 + ej); }
+        if (b1 + ej < e1) { ent1 = __ldg(p.entries + b1 + ej); val1 = __ldg(p.ovals + b1 + ej); }
         bool ok = true;
-        for (int it = ph; it < KT && ok; it += 4) {
-            // prefetch: the entries of the next step (their range arrived a step ago) and the range of the one after
-            uint32_t ent1 = 0, val1 = 0;
-            const bool has1 = b1 + ej < e1;
-            if (has1) { ent1 = __ldg(p.entries + b1 + ej); val1 = __ldg(p.ovals + b1 + ej); }
-            int b2 = 0, e2 = 0;
-            if (it + 8 < KT) { b2 = __ldg(cp + it + 8); e2 = __ldg(cp + it + 9); }
+        for (int n = 0; n < nsteps && ok; ++n) {
+            const int it = ph + 4 * n;
+            // request the entries of step n + 2; when that step opens a new block of ranges, refill the idle block
+            int b2, e2;
+            range_of(n + 2, b2, e2);
+            uint32_t ent2 = 0, val2 = 0;
+            if (b2 + ej < e2) { ent2 = __ldg(p.entries + b2 + ej); val2 = __ldg(p.ovals + b2 + ej); }
+            if (((n + 2) & 15) == 0) {
+                const int block = (n + 2) >> 4;
+                if (block & 1) load_ranges(block + 1, rbA, reA); else load_ranges(block + 1, rbB, reB);
+            }
+            const uint32_t pk0 = b0 + ej < e0 ? pack(ent0, val0) : NO_ENTRY;
 
             const int sc_ = it % GM_CS, cround = it / GM_CS;   // code slot
             const int around = it / GM_XS;                     // use count of A stage ph
@@ -425,13 +461,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
                 }
             }
             // the A stage must have been read by the MMAs of its previous use
-            if (around > 0 && !mbar_wait_warp<100>(mma_done(ph), (around - 1) & 1, s_abort)) { ok = false; break; }
+            if (around > 0 && !mbar_wait_warp<40>(mma_done(ph), (around - 1) & 1, s_abort)) { ok = false; break; }
             tcgen05_fence_after();
             tmem_st_32x32b_x32(taddr, o);
             tmem_st_wait();
             tcgen05_fence_before();
-            mbar_arrive(aready_bar(ph));
-            pk0 = has1 ? pack(ent1, val1) : NO_ENTRY;
+            mbar_arrive(ready_bar(ph));
+            ent0 = ent1; val0 = val1; ent1 = ent2; val1 = val2;
             b0 = b1; e0 = e1; b1 = b2; e1 = e2;
         }
         if (!ok) *s_abort = 1;
