@@ -306,14 +306,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             // issued between the MMAs of this one (its result is only looked at afterwards) and nothing but the
             // commit stands between the last MMA of a step and the first of the next.
             bool ok = KT > 0 && mbar_wait(ready_bar(0), 0);
-            uint64_t db[GM_XS];
-#pragma unroll
-            for (int s = 0; s < GM_XS; ++s) db[s] = make_smem_desc(base + OFF_B + s * B_BYTES);
+            const uint64_t db0 = make_smem_desc(base + OFF_B);
             const uint32_t ta0 = tmem_base + (uint32_t)BN;
             for (int it = 0; it < KT && ok; ++it) {
                 const int s = it % GM_XS;
                 tcgen05_fence_after();
-                const uint64_t dbs = db[s];
+                const uint64_t dbs = db0 + (uint64_t)((s * B_BYTES) >> 4);   // the address field counts 16-byte units
                 const uint32_t ta = ta0 + (uint32_t)(s * GM_A_COLS);
                 umma_f16_ts(tmem_base, ta, dbs, gm_idesc<BN>(), it != 0);
                 umma_f16_ts(tmem_base, ta + 8u, dbs + 2u, gm_idesc<BN>(), 1u);
