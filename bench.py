@@ -12,16 +12,20 @@ streams far more than the 126 MB L2, so nothing is served from cache).
   value     algorithmic bytes of a step / device time, inputs resident in HBM,
             the step replayed from a CUDA graph (one launch per linear)
   e2e       the same pass through QuantizedLinear.forward with host activations:
-            per linear a pinned-host -> device copy of x and a device -> host
-            read of y inside the timed region
+            every step copies the activations from pinned host memory to the
+            device, replays a CUDA graph captured from the 224 module calls and
+            copies all 224 outputs back to pinned host memory, inside the timed
+            region (`extra.e2e_eager_gbs`: the same with copy-in, call and
+            copy-out issued per linear from Python, no graph)
   extra     the other two figures BASELINE.json names (prefill GEMM TFLOP/s,
             quantize GB/s), GEMV at batch 4 and 16 and, with --gpus > 1, the
             70B-shaped column-parallel decode (batch 32, NCCL all-gather)
 
 With --gpus N > 1 every rank runs the same pass on its own GPU (replicas, no
 collective: the path shards by independent tensors) and `value` is the sum over
-ranks / max time over ranks ("weak").  --impl reference times the CPU oracle
-port of the same linears on the host cores (rank 0 only).
+ranks / max time over ranks ("weak").  --impl reference times the reference's
+forward on the host cores (rank 0 only): torch CPU F.linear on the cached fp16
+weight, with the first-call dequantization (CPU oracle port) reported beside it.
 """
 from __future__ import annotations
 
@@ -222,25 +226,52 @@ def measure_gemv(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16):
     return nbytes, secs, len(model)
 
 
-def measure_e2e(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16):
-    """The decode pass through QuantizedLinear.forward with host-resident activations."""
+def measure_e2e(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16, eager=False):
+    """The decode pass through the public module API (`QuantizedLinear.forward`) with host-resident activations.
+
+    Every step copies the step's activations from pinned host memory to the device, runs the 224 module
+    calls and copies all 224 outputs back to pinned host memory, then waits for them.  Default: the module
+    calls are captured once in a CUDA graph (the way a serving loop drives a decode step) that reads static
+    input tensors; `eager=True` instead issues copy-in, call, copy-out per linear from Python."""
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator().manual_seed(11)
     hx = {k: torch.randn(m, k, generator=gen).to(dtype).pin_memory() for k in {l.k for _, l in model}}
-    hy = {n: torch.empty(m, n, dtype=dtype).pin_memory() for n in {l.n for _, l in model}}
+    nbytes = sum(linear_bytes(l.n, l.k, l.n_out, m) for _, l in model)
+    if eager:
+        hy = {n: torch.empty(m, n, dtype=dtype).pin_memory() for n in {l.n for _, l in model}}
+
+        def one_pass():
+            for _, lin in model:
+                x = hx[lin.k].to(dev, non_blocking=True)
+                y = lin.module(x)
+                hy[lin.n].copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()  # the caller holds y on the host
+
+        secs = time_steps(one_pass, steps, warmup, barrier)
+        return nbytes, secs, sum(m * l.k * 2 for _, l in model), sum(m * l.n * 2 for _, l in model)
+
+    dx = {k: torch.empty(m, k, dtype=dtype, device=dev) for k in hx}
+    total_out = sum(m * l.n for _, l in model)
+    hy = torch.empty(total_out, dtype=dtype).pin_memory()
+    for k in hx:
+        dx[k].copy_(hx[k])
+    for _, lin in model[:8]:
+        lin.module(dx[lin.k])           # warm the call path before capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = [lin.module(dx[lin.k]) for _, lin in model]
+        flat = torch.cat([o.reshape(-1) for o in outs])
 
     def one_pass():
-        for _, lin in model:
-            x = hx[lin.k].to(dev, non_blocking=True)
-            y = lin.module(x)
-            hy[lin.n].copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller holds y on the host
+        for k in hx:
+            dx[k].copy_(hx[k], non_blocking=True)
+        graph.replay()
+        hy.copy_(flat, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller holds every output on the host
 
     secs = time_steps(one_pass, steps, warmup, barrier)
-    h2d = sum(m * l.k * 2 for _, l in model)
-    d2h = sum(m * l.n * 2 for _, l in model)
-    nbytes = sum(linear_bytes(l.n, l.k, l.n_out, m) for _, l in model)
-    return nbytes, secs, h2d, d2h
+    return nbytes, secs, sum(m * k * 2 for k in hx), total_out * 2
 
 
 def measure_gemm(steps, warmup):
@@ -484,6 +515,8 @@ def run_ours(args, rank, world, local_rank):
 
     extra = {}
     if rank == 0 and not args.headline_only:
+        eb, es, _, _ = measure_e2e(model, 1, max(2, args.steps // 5), 2, eager=True)
+        extra["e2e_eager_gbs"] = eb * max(2, args.steps // 5) / es / 1e9   # copy-in, call, copy-out per linear from Python
         for m in (4, 16):
             b, s, _ = measure_gemv(model, m, max(2, args.steps // 2), 3)
             extra[f"decode_m{m}_gbs"] = b * max(2, args.steps // 2) / s / 1e9
@@ -521,7 +554,9 @@ def run_ours(args, rank, world, local_rank):
             warmup=args.warmup, ms_per_step=secs / args.steps * 1e3, higher_is_better=True, scaling="weak",
             vs_baseline=None, dtype="int8 codes x fp16 scales -> fp16 MMA, fp32 accumulate", data="synthetic",
             config=dict(workload_config(1), layers=args.layers), clocks=clocks,
-            e2e=dict(value=e2e_value, unit="GB/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+            e2e=dict(value=e2e_value, unit="GB/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                     method="per step: pinned-host activations -> device, CUDA-graph replay of the 224 "
+                            "QuantizedLinear.forward calls, all 224 outputs -> pinned host, wait"),
             gpu_launches=launches * args.steps,
             roofline=dict(bound="hbm", achieved=per_gpu, peak=pk["hbm"], unit="GB/s", frac=per_gpu / pk["hbm"],
                           # DRAM bytes per launch, averaged over the step's launches: ncu measured 17.43 MB for a
