@@ -683,9 +683,16 @@ extern "C" int atlas_qlinear_gemv(const void *x, int dtype, int64_t m, int64_t l
         p.status = status;
         p.bs_shift = (block_size & (block_size - 1)) == 0 ? __builtin_ctz((unsigned)block_size) : -1;
 
-        if (mt == 1 && p.x_vec_ok) {
-            rc = launch_gemv_strip(p, st);
-            if (rc) return rc;
+        if (mt <= 2 && p.x_vec_ok) {
+            // up to 16 rows: one strip-kernel launch per 8 rows (the second pass over a weight finds most of it in L2)
+            for (int r0 = 0; r0 < mg; r0 += 8) {
+                GemvParams ps = p;
+                ps.m = mg - r0 < 8 ? mg - r0 : 8;
+                ps.x = (const char *)p.x + (size_t)r0 * ldx * 2;
+                ps.y = (char *)p.y + (size_t)r0 * ldy * 2;
+                rc = launch_gemv_strip(ps, st);
+                if (rc) return rc;
+            }
             continue;
         }
         const int mtot = mt * 8;

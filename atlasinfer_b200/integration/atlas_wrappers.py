@@ -22,7 +22,7 @@ from .. import _capi
 from ..quant.adaptive_quantizer import QuantizedTensor
 
 # rows of x up to which the CUDA-core-issued streaming kernel is used; above it the tcgen05 kernel
-GEMV_MAX_ROWS = 8
+GEMV_MAX_ROWS = 16
 
 _VERBOSE = os.environ.get("ATLAS_VERBOSE", "0") not in ("", "0")
 
