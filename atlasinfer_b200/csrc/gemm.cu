@@ -10,9 +10,9 @@
 // One CTA computes a 128 (output features) x BN (tokens) tile.  The rebuilt fp16 weights never touch
 // shared memory: the dequantizer warps write them straight into tensor memory and the MMA takes its A
 // operand from there, so shared memory only carries what comes from global memory (the kernel is bound
-// by the shared-memory data pipe, not by the tensor pipe).  Rings: codes (8 slots of 8 KB + 256 B of
-// scales: they come from HBM and need the deepest prefetch), activations (4 slots of BN x 64 fp16,
-// L2-resident), rebuilt weights (4 stages of 32 TMEM columns beside the accumulator).
+// by the shared-memory data pipe, not by the tensor pipe).  A pipeline stage is two k-tiles (128 columns
+// of K).  Rings: codes (4 stages of 2 x (8 KB + 256 B of scales)), activations (2 stages of 2 x BN x 64
+// fp16, L2-resident), rebuilt weights (4 stages of 64 TMEM columns beside the accumulator; 2 for BN < 256).
 //   warp 0      activation producer: per 64-wide K step a 2-D TMA load of the BN x 64 fp16
 //               activation tile (128-byte swizzle) completing on the step's `ready` barrier
 //   warp 2      code producer: a 1-D bulk copy of the step's 8 KB code tile (contiguous in the
@@ -29,7 +29,7 @@
 //               fp32 accumulate in TMEM) four times per step and commits the slot's `mma_done`
 //               mbarrier (which frees both the activation slot and the A stage); after the last step
 //               it commits `acc_full`
-//   warps 3-10  epilogue: tcgen05.ld of their TMEM lane quarter (two warps per quarter, half of
+//   warps 3-18  epilogue: tcgen05.ld of their TMEM lane quarter (four warps per quarter, a quarter of
 //               the columns each), + bias, convert, transpose through shared memory, 16-byte stores
 // Every mbarrier wait is bounded; if one runs out the CTA sets the caller's status word,
 // skips the rest of its work, frees its TMEM and returns.
@@ -45,30 +45,33 @@ namespace atlas {
 namespace {
 
 constexpr int GM_DQ_WARPS = 16;                      // dequantizer warps: 4 TMEM lane quarters x 4 K-step phases
-constexpr int GM_EPI_WARPS = 8;                      // the first eight of them drain the accumulator
+constexpr int GM_EPI_WARPS = 16;                     // all of them drain the accumulator: four per TMEM lane quarter
 constexpr int GM_CTRL_WARPS = 3;                     // activation producer, MMA issuer, code producer
 constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_WARPS) * 32;
 constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
 constexpr int GM_BK = 64;   // K per pipeline step (one 128-byte swizzle row of fp16)
-constexpr int GM_XS = 4;    // activation ring depth = A stages in tensor memory = K-step phases of the dequantizers
-constexpr int GM_CS = 8;    // code ring depth
-constexpr int GM_A_COLS = GM_BK / 2;             // TMEM columns of one A stage: two fp16 per 32-bit cell
+constexpr int GM_SK = 2;    // k-tiles per pipeline stage: one barrier round trip, poll and commit per 128 columns of K
+constexpr int GM_XS = 2;    // activation ring depth, in stages
+constexpr int GM_CS = 4;    // code ring depth, in stages
+constexpr int GM_PH = 4;    // K-stage phases of the dequantizers = `ready` / `mma_done` barriers
+constexpr int GM_A_COLS = GM_SK * GM_BK / 2;     // TMEM columns of one A stage: two fp16 per 32-bit cell
 constexpr uint32_t C_BYTES = GM_BM * GM_BK;      // 8 KB code tile
 constexpr uint32_t S_BYTES = 256;                // one scale block: 128 rows x fp16
-static_assert(GM_XS == 4, "a dequantizer warp owns the A stage of its phase");
 // shared-memory map for a tile of BN tokens (BN = 32, 64, 128 or 256 = UMMA N)
 template <int BN>
 struct Smem {
-    static constexpr uint32_t B_BYTES = BN * GM_BK * 2;   // fp16 activation tile
+    static constexpr uint32_t B_BYTES = BN * GM_BK * 2;   // fp16 activation tile of one k-tile
     static constexpr uint32_t OFF_B = 0;
-    static constexpr uint32_t OFF_C = OFF_B + GM_XS * B_BYTES;
-    static constexpr uint32_t OFF_BAR = OFF_C + GM_CS * C_BYTES;
+    static constexpr uint32_t OFF_C = OFF_B + GM_XS * GM_SK * B_BYTES;
+    static constexpr uint32_t OFF_BAR = OFF_C + GM_CS * GM_SK * C_BYTES;
     static constexpr uint32_t OFF_S = OFF_BAR + 256;
-    static constexpr uint32_t TOTAL = OFF_S + GM_CS * S_BYTES + 1024 /*alignment slack*/;
-    // accumulator columns [0, BN), A stages [BN, BN + 4 * 32); allocations are powers of two
-    static constexpr uint32_t TMEM_COLS = BN + GM_XS * GM_A_COLS <= 256 ? 256 : 512;
+    static constexpr uint32_t TOTAL = OFF_S + GM_CS * GM_SK * S_BYTES + 1024 /*alignment slack*/;
+    // A stages in tensor memory (64 columns each) beside the accumulator columns [0, BN); allocations are powers of two
+    static constexpr int A_STAGES = BN == 256 ? 4 : 2;
+    static constexpr uint32_t TMEM_COLS = BN + A_STAGES * GM_A_COLS <= 256 ? 256 : 512;
+    static_assert(BN + A_STAGES * GM_A_COLS <= 512, "tensor memory");
     // the epilogue stages the output tile over the (then idle) activation and code rings
-    static_assert((BN * (GM_BM + 4)) * 4 <= GM_XS * B_BYTES + GM_CS * C_BYTES, "epilogue staging does not fit");
+    static_assert((BN * (GM_BM + 4)) * 4 <= GM_XS * GM_SK * B_BYTES + GM_CS * GM_SK * C_BYTES, "epilogue staging does not fit");
 };
 constexpr int GM_SPIN_LIMIT = 1 << 20;       // polls per wait
 
@@ -228,14 +231,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     // ready(s): the activation tile has landed (one arrival + its bytes) and the four dequantizer warps of the
     // stage have stored the weights (128 arrivals); the MMA thread waits on this one barrier per K step
     auto ready_bar = [&](int s) { return bars + 8u * s; };
-    auto mma_done = [&](int s) { return bars + 8u * (GM_XS + s); };
-    auto full_c = [&](int s) { return bars + 8u * (2 * GM_XS + s); };
-    auto empty_c = [&](int s) { return bars + 8u * (2 * GM_XS + GM_CS + s); };
-    constexpr int N_BARS = 2 * GM_XS + 2 * GM_CS + 1;
+    auto mma_done = [&](int s) { return bars + 8u * (GM_PH + s); };
+    auto full_c = [&](int s) { return bars + 8u * (2 * GM_PH + s); };
+    auto empty_c = [&](int s) { return bars + 8u * (2 * GM_PH + GM_CS + s); };
+    constexpr int N_BARS = 2 * GM_PH + 2 * GM_CS + 1;
     static_assert(N_BARS * 8 + 16 <= 256, "barrier area");
     const uint32_t accfull_bar = bars + 8u * (N_BARS - 1);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + OFF_BAR + 8 * N_BARS);
     volatile int *s_abort = reinterpret_cast<volatile int *>(base_ptr + OFF_BAR + 8 * N_BARS + 8);
+    constexpr int AS = SM::A_STAGES;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * GM_BM;  // first weight row (output feature) of the tile
@@ -243,9 +247,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     // this CTA's K steps (grid.z slices K)
     const int kt_begin = (int)((long long)p.k_tiles * blockIdx.z / p.splits);
     const int KT = (int)((long long)p.k_tiles * (blockIdx.z + 1) / p.splits) - kt_begin;
+    const int NST = (KT + GM_SK - 1) / GM_SK;   // pipeline stages of GM_SK k-tiles (the last one may hold a single k-tile)
+    // stage st uses barriers ready[st % 4] / mma_done[st % 4] in round st / 4, activation slot st % GM_XS, code slot
+    // st % GM_CS and A stage st % AS; a resource used by stage st is free again when mma_done of stage st fired
+    auto done_bar_of = [&](int st) { return mma_done(st % GM_PH); };
+    auto done_par_of = [&](int st) { return (uint32_t)((st / GM_PH) & 1); };
 
+    if (tid == 32 * 0 + 1 || tid == 32 * 2 + 1) {   // the TMA units fetch the 128-byte tensor maps on first use: start that now
+        asm volatile("prefetch.tensormap [%0];" ::"l"(tid < 32 ? (const void *)&x_map : (const void *)&c_map) : "memory");
+    }
     if (tid == 0) {
-        for (int s = 0; s < GM_XS; ++s) {
+        for (int s = 0; s < GM_PH; ++s) {
             mbar_init(ready_bar(s), 4 * 32 + 1);
             mbar_init(mma_done(s), 1);
         }
@@ -272,12 +284,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
         if (lane == 0) {
             // activations come from earlier kernels of the stream; everything else so far read only weights
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (int it = 0; it < KT; ++it) {
-                const int s = it % GM_XS, round = it / GM_XS;
-                if (round > 0 && !mbar_wait<32>(mma_done(s), (round - 1) & 1)) { *s_abort = 1; break; }
+            for (int st = 0; st < NST; ++st) {
+                const int slot = st % GM_XS;
+                if (st >= GM_XS && !mbar_wait<32>(done_bar_of(st - GM_XS), done_par_of(st - GM_XS))) { *s_abort = 1; break; }
                 if (*s_abort) break;
-                mbar_arrive_expect_tx(ready_bar(s), B_BYTES);
-                tma_load_2d(base + OFF_B + s * B_BYTES, &x_map, (kt_begin + it) * GM_BK, m0, ready_bar(s));
+                const int nk = min(GM_SK, KT - st * GM_SK);
+                const uint32_t rb = ready_bar(st % GM_PH);
+                mbar_arrive_expect_tx(rb, (uint32_t)nk * B_BYTES);
+                for (int j = 0; j < nk; ++j)
+                    tma_load_2d(base + OFF_B + (slot * GM_SK + j) * B_BYTES, &x_map, (kt_begin + st * GM_SK + j) * GM_BK, m0, rb);
             }
         }
     } else if (warp == 2) {
@@ -285,45 +300,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
         if (lane == 0) {
             const int64_t crow0 = (int64_t)blockIdx.x * p.k_tiles + kt_begin;   // code tiles are rows of 128 in the map
             const int bpr = p.n_cols / p.bs;
-            for (int it = 0; it < KT; ++it) {
-                const int s = it % GM_CS, round = it / GM_CS;
-                if (round > 0 && !mbar_wait<200>(empty_c(s), (round - 1) & 1)) { *s_abort = 1; break; }
+            for (int st = 0; st < NST; ++st) {
+                const int slot = st % GM_CS, round = st / GM_CS;
+                if (round > 0 && !mbar_wait<200>(empty_c(slot), (round - 1) & 1)) { *s_abort = 1; break; }
                 if (*s_abort) break;
-                mbar_arrive_expect_tx(full_c(s), C_BYTES + (p.bs_tiles ? S_BYTES : 0));
-                // the 8 KB code tile is a 128-row x 64-byte matrix; the 64-byte swizzle spreads a column of 16-byte
-                // chunks over all banks for the dequantizers (thread = row)
-                tma_load_2d(base + OFF_C + s * C_BYTES, &c_map, 0, (int)((crow0 + it) * GM_BM), full_c(s));
-                if (p.bs_tiles)
-                    bulk_load_1d(base + OFF_S + s * S_BYTES,
-                                 p.scales_t + ((size_t)blockIdx.x * bpr + (kt_begin + it) / p.bs_tiles) * 128, S_BYTES, full_c(s));
+                const int nk = min(GM_SK, KT - st * GM_SK);
+                mbar_arrive_expect_tx(full_c(slot), (uint32_t)nk * (C_BYTES + (p.bs_tiles ? S_BYTES : 0)));
+                for (int j = 0; j < nk; ++j) {
+                    const int kt = st * GM_SK + j;
+                    // an 8 KB code tile is a 128-row x 64-byte matrix; the 64-byte swizzle spreads a column of 16-byte
+                    // chunks over all banks for the dequantizers (thread = row)
+                    tma_load_2d(base + OFF_C + (slot * GM_SK + j) * C_BYTES, &c_map, 0, (int)((crow0 + kt) * GM_BM), full_c(slot));
+                    if (p.bs_tiles)
+                        bulk_load_1d(base + OFF_S + (slot * GM_SK + j) * S_BYTES,
+                                     p.scales_t + ((size_t)blockIdx.x * bpr + (kt_begin + kt) / p.bs_tiles) * 128, S_BYTES, full_c(slot));
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            // One barrier poll, four MMAs and one commit per K step.  An MMA issue, a poll and a commit each cost this
-            // single thread 70-180 cycles; the tensor pipe needs 4 x 128 for the step, so the poll for the next step is
-            // issued between the MMAs of this one (its result is only looked at afterwards) and nothing but the
-            // commit stands between the last MMA of a step and the first of the next.
-            bool ok = KT > 0 && mbar_wait(ready_bar(0), 0);
+            // One barrier poll, eight MMAs and one commit per stage.  An MMA issue, a poll and a commit each cost this
+            // single thread 70-180 cycles and the tensor pipe needs 128 cycles per MMA, so the poll for the next stage
+            // is issued between the MMAs of this one (its result is only looked at afterwards) and nothing but the
+            // commit stands between the last MMA of a stage and the first of the next.
+            bool ok = NST > 0 && mbar_wait(ready_bar(0), 0);
             const uint64_t db0 = make_smem_desc(base + OFF_B);
             const uint32_t ta0 = tmem_base + (uint32_t)BN;
-            for (int it = 0; it < KT && ok; ++it) {
-                const int s = it % GM_XS;
+            for (int st = 0; st < NST && ok; ++st) {
                 tcgen05_fence_after();
-                const uint64_t dbs = db0 + (uint64_t)((s * B_BYTES) >> 4);   // the address field counts 16-byte units
-                const uint32_t ta = ta0 + (uint32_t)(s * GM_A_COLS);
-                umma_f16_ts(tmem_base, ta, dbs, gm_idesc<BN>(), it != 0);
+                const uint64_t dbs = db0 + (uint64_t)(((st % GM_XS) * GM_SK * B_BYTES) >> 4);   // the address field counts 16-byte units
+                const uint32_t ta = ta0 + (uint32_t)((st % AS) * GM_A_COLS);
+                const bool two = KT - st * GM_SK >= 2;
+                umma_f16_ts(tmem_base, ta, dbs, gm_idesc<BN>(), st != 0);
                 umma_f16_ts(tmem_base, ta + 8u, dbs + 2u, gm_idesc<BN>(), 1u);
-                // the next step's barrier: one poll now, looked at after the commit
-                const int sn = (it + 1) % GM_XS;
-                const uint32_t pn = ((it + 1) / GM_XS) & 1;
-                const bool next_ready = it + 1 < KT ? mbar_try_wait(ready_bar(sn), pn) : true;
+                // the next stage's barrier: one poll now, looked at after the commit
+                const uint32_t rbn = ready_bar((st + 1) % GM_PH);
+                const uint32_t pn = (uint32_t)(((st + 1) / GM_PH) & 1);
+                const bool next_ready = st + 1 < NST ? mbar_try_wait(rbn, pn) : true;
                 umma_f16_ts(tmem_base, ta + 16u, dbs + 4u, gm_idesc<BN>(), 1u);
                 umma_f16_ts(tmem_base, ta + 24u, dbs + 6u, gm_idesc<BN>(), 1u);
-                umma_commit(mma_done(s));  // arrives when these MMAs have finished reading the slot and the A stage
-                if (!next_ready) ok = mbar_wait(ready_bar(sn), pn);
-                if ((it & 15) == 15 && *s_abort) ok = false;
+                if (two) {
+                    const uint64_t db1 = dbs + (uint64_t)(B_BYTES >> 4);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma_f16_ts(tmem_base, ta + 32u + (uint32_t)(k * 8), db1 + (uint64_t)(k * 2), gm_idesc<BN>(), 1u);
+                }
+                umma_commit(done_bar_of(st));  // arrives when these MMAs have finished reading the slot and the A stage
+                if (!next_ready) ok = mbar_wait(rbn, pn);
+                if ((st & 7) == 7 && *s_abort) ok = false;
             }
             if (!ok) *s_abort = 1;
             umma_commit(accfull_bar);  // arrives when every MMA issued so far is complete
@@ -343,25 +367,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
         const int32_t *cp = p.chunk_ptr + strip * (p.n_chunks + 1) + kt_begin;
         const int ej = lane & 15;                 // which entry of its strip's list this lane buffers
         const uint32_t code_off = (uint32_t)rl * 64u;   // the tile is a 128 x 64-byte row-major matrix
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)BN + (uint32_t)(ph * GM_A_COLS);
-        // Side-table pipeline.  The warp's steps are numbered n = 0, 1, .. (K step it = ph + 4 n).  The entry ranges
-        // [cp[it], cp[it + 1]) of 16 consecutive steps sit in one register per lane (lane j of each half-warp: step
-        // 16 * block + j of its strip), two such blocks alternate; the entries of a step are requested two steps
-        // ahead, one per lane, and packed for the patch when the step starts: owner lane (strip half * 16 + row)
-        // << 22 | column inside the K step << 16 | fp16 value; 63 in the lane field matches nobody.
-        auto pack = [&](uint32_t ent, uint32_t val) -> uint32_t {
-            return ((uint32_t)(lane & 16) | (ent >> 24)) << 22 | (ent & 63u) << 16 | val;
-        };
-        constexpr uint32_t NO_ENTRY = 63u << 22;
-        const int nsteps = ph < KT ? (KT - ph + 3) >> 2 : 0;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)BN + (uint32_t)((ph % AS) * GM_A_COLS);
+        // Side-table pipeline.  The warp's stages are numbered n = 0, 1, .. (stage st = ph + 4 n = k-tiles 2 st, 2 st + 1).
+        // The entry ranges [cp[2 st], cp[2 st + 2]) of 16 consecutive stages sit in one register per lane (lane j of each
+        // half-warp: stage 16 * block + j of its strip), two such blocks alternate; the entries of a stage are requested
+        // two stages ahead, one per lane, and packed for the patch when the stage starts: owner lane (strip half * 16 +
+        // row) << 23 | column inside the stage (0..127) << 16 | fp16 value; 63 in the lane field matches nobody.
+        constexpr uint32_t NO_ENTRY = 63u << 23;
+        const int nsteps = ph < NST ? (NST - ph + 3) >> 2 : 0;
         int rbA = 0, reA = 0, rbB = 0, reB = 0;
         auto load_ranges = [&](int block, int &rb, int &re) {
             const int nn = block * 16 + ej;
             rb = 0;
             re = 0;
-            if (nn < nsteps) { rb = __ldg(cp + ph + 4 * nn); re = __ldg(cp + ph + 4 * nn + 1); }
+            if (nn < nsteps) {
+                const int kt = (ph + 4 * nn) * GM_SK;
+                rb = __ldg(cp + kt);
+                re = __ldg(cp + min(kt + GM_SK, KT));
+            }
         };
-        auto range_of = [&](int nn, int &b_, int &e_) {   // ranges of step nn for both half-warps; (0, 0) past the end
+        auto range_of = [&](int nn, int &b_, int &e_) {   // ranges of stage nn for both half-warps; (0, 0) past the end
             const bool odd = (nn >> 4) & 1;
             const int src = (lane & 16) | (nn & 15);
             b_ = __shfl_sync(0xffffffffu, odd ? rbB : rbA, src);
@@ -377,8 +402,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
         if (b1 + ej < e1) { ent1 = __ldg(p.entries + b1 + ej); val1 = __ldg(p.ovals + b1 + ej); }
         bool ok = true;
         for (int n = 0; n < nsteps && ok; ++n) {
-            const int it = ph + 4 * n;
-            // request the entries of step n + 2; when that step opens a new block of ranges, refill the idle block
+            const int st = ph + 4 * n;
+            // request the entries of stage n + 2; when that stage opens a new block of ranges, refill the idle block
             int b2, e2;
             range_of(n + 2, b2, e2);
             uint32_t ent2 = 0, val2 = 0;
@@ -387,84 +412,100 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
                 const int block = (n + 2) >> 4;
                 if (block & 1) load_ranges(block + 1, rbA, reA); else load_ranges(block + 1, rbB, reB);
             }
-            const uint32_t pk0 = b0 + ej < e0 ? pack(ent0, val0) : NO_ENTRY;
-
-            const int sc_ = it % GM_CS, cround = it / GM_CS;   // code slot
-            const int around = it / GM_XS;                     // use count of A stage ph
-            if (!mbar_wait_warp<40>(full_c(sc_), cround & 1, s_abort)) { ok = false; break; }
-            const unsigned char *codes = base_ptr + OFF_C + sc_ * C_BYTES + code_off;
-            const int k0 = (kt_begin + it) * GM_BK;
-            // the row's 64 codes: chunk c sits at c ^ ((row >> 1) & 3) under the 64-byte swizzle, so the 8 lanes of a
-            // quarter-warp (rows 64 bytes apart) cover all 32 banks
-            uint4 L[4];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) L[c] = *reinterpret_cast<const uint4 *>(codes + ((c ^ swz) << 4));
-            __half sh[4];
-            if (p.bs_tiles) {
-                const uint16_t *scs = reinterpret_cast<const uint16_t *>(base_ptr + OFF_S + sc_ * S_BYTES);
-                sh[0] = sh[1] = sh[2] = sh[3] = __ushort_as_half(scs[rl]);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    sh[c] = __ushort_as_half(__ldg(sc_tile + (int64_t)((k0 + c * 16) / p.bs) * 128 + rl));
-            }
-            // the code slot is in registers: hand it back (one arrival per warp)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty_c(sc_));
-            uint32_t o[32];   // the row's 64 fp16 weights of this K step, two per register
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const __half2 s2 = __half2half2(sh[c]);
-                dequant4(L[c].x, s2, o[c * 8 + 0], o[c * 8 + 1]);
-                dequant4(L[c].y, s2, o[c * 8 + 2], o[c * 8 + 3]);
-                dequant4(L[c].z, s2, o[c * 8 + 4], o[c * 8 + 5]);
-                dequant4(L[c].w, s2, o[c * 8 + 6], o[c * 8 + 7]);
-            }
-            // outliers of the two strips inside this K step.  Every lane finds the buffered entries of its own row
-            // (five ballots over the owner field), pulls them with one shuffle per round and puts the raw fp16 value
-            // over the zero-coded slot; the rounds are the largest number of outliers any row has in this step.
-            auto put = [&](uint32_t pk, bool have) {
-                const uint32_t onehot = have ? 1u << ((pk >> 17) & 31u) : 0u;      // which of the row's 32 registers
-                const uint32_t sel = (pk & 0x10000u) ? 0x5410u : 0x3254u;          // odd column: high half, even: low half
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (onehot & (1u << i)) o[i] = __byte_perm(o[i], pk, sel);
+            const int k0 = (kt_begin + st * GM_SK) * GM_BK;   // first column of the stage
+            const int nk = min(GM_SK, KT - st * GM_SK);
+            auto pack = [&](uint32_t owner_base, uint32_t ent, uint32_t val) -> uint32_t {
+                return (owner_base | (ent >> 24)) << 23 | ((ent & 0xffffffu) - (uint32_t)k0) << 16 | val;
             };
+            const uint32_t pk0 = b0 + ej < e0 ? pack((uint32_t)(lane & 16), ent0, val0) : NO_ENTRY;
+            // which buffered entries belong to this lane's row: five ballots over the owner field
+            uint32_t mine_all;
             {
-                const uint32_t own = pk0 >> 22;   // owner lane of the entry this lane buffers, 63: none
-                uint32_t mine = __ballot_sync(0xffffffffu, own != 63u);
+                const uint32_t own = pk0 >> 23;
+                mine_all = __ballot_sync(0xffffffffu, own != 63u);
 #pragma unroll
                 for (int bit = 0; bit < 5; ++bit) {
                     const uint32_t bb = __ballot_sync(0xffffffffu, (own >> bit) & 1u);
-                    mine &= ((lane >> bit) & 1) ? bb : ~bb;
-                }
-                const int rounds = __reduce_max_sync(0xffffffffu, __popc(mine));
-                for (int r = 0; r < rounds; ++r) {
-                    const bool have = mine != 0;
-                    const uint32_t pk = __shfl_sync(0xffffffffu, pk0, have ? __ffs(mine) - 1 : 0);
-                    mine &= mine - 1;
-                    put(pk, have);
+                    mine_all &= ((lane >> bit) & 1) ? bb : ~bb;
                 }
             }
+            const uint32_t second = __ballot_sync(0xffffffffu, (pk0 >> 22) & 1u);   // entries of the stage's second k-tile
+
+            const int sc_ = st % GM_CS, cround = st / GM_CS;   // code slot
+            if (!mbar_wait_warp<40>(full_c(sc_), cround & 1, s_abort)) { ok = false; break; }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {   // rare: more than 16 outliers of one strip inside one K step
-                const int cnt = __shfl_sync(0xffffffffu, e0 - b0, h * 16);
-                if (cnt > 16) {
-                    const int bb = __shfl_sync(0xffffffffu, b0, h * 16);
-                    for (int j = 16; j < cnt; ++j) {
-                        const uint32_t ent = __ldg(p.entries + bb + j);
-                        const uint32_t pk = ((uint32_t)(h * 16) | (ent >> 24)) << 22 | (ent & 63u) << 16 | (uint32_t)__ldg(p.ovals + bb + j);
-                        put(pk, (pk >> 22) == (uint32_t)lane);
+            for (int j = 0; j < GM_SK; ++j) {
+                if (j < nk) {
+                    const unsigned char *codes = base_ptr + OFF_C + (sc_ * GM_SK + j) * C_BYTES + code_off;
+                    // the row's 64 codes: chunk c sits at c ^ ((row >> 1) & 3) under the 64-byte swizzle, so the 8 lanes
+                    // of a quarter-warp (rows 64 bytes apart) cover all 32 banks
+                    uint4 L[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) L[c] = *reinterpret_cast<const uint4 *>(codes + ((c ^ swz) << 4));
+                    __half sh[4];
+                    if (p.bs_tiles) {
+                        const uint16_t *scs = reinterpret_cast<const uint16_t *>(base_ptr + OFF_S + (sc_ * GM_SK + j) * S_BYTES);
+                        sh[0] = sh[1] = sh[2] = sh[3] = __ushort_as_half(scs[rl]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            sh[c] = __ushort_as_half(__ldg(sc_tile + (int64_t)((k0 + j * GM_BK + c * 16) / p.bs) * 128 + rl));
                     }
+                    if (j == nk - 1) {   // the code slot is in registers: hand it back (one arrival per warp)
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty_c(sc_));
+                    }
+                    uint32_t o[32];   // the row's 64 fp16 weights of this k-tile, two per register
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const __half2 s2 = __half2half2(sh[c]);
+                        dequant4(L[c].x, s2, o[c * 8 + 0], o[c * 8 + 1]);
+                        dequant4(L[c].y, s2, o[c * 8 + 2], o[c * 8 + 3]);
+                        dequant4(L[c].z, s2, o[c * 8 + 4], o[c * 8 + 5]);
+                        dequant4(L[c].w, s2, o[c * 8 + 6], o[c * 8 + 7]);
+                    }
+                    // outliers of the two strips inside this k-tile: every lane pulls the buffered entries of its own row
+                    // with one shuffle per round and puts the raw fp16 value over the zero-coded slot; the rounds are
+                    // the largest number of outliers any row has in this k-tile
+                    auto put = [&](uint32_t pk, bool have) {
+                        const uint32_t onehot = have ? 1u << ((pk >> 17) & 31u) : 0u;      // which of the row's 32 registers
+                        const uint32_t sel = (pk & 0x10000u) ? 0x5410u : 0x3254u;          // odd column: high half, even: low half
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (onehot & (1u << i)) o[i] = __byte_perm(o[i], pk, sel);
+                    };
+                    {
+                        uint32_t mine = mine_all & (j == 0 ? ~second : second);
+                        const int rounds = __reduce_max_sync(0xffffffffu, __popc(mine));
+                        for (int r = 0; r < rounds; ++r) {
+                            const bool have = mine != 0;
+                            const uint32_t pk = __shfl_sync(0xffffffffu, pk0, have ? __ffs(mine) - 1 : 0);
+                            mine &= mine - 1;
+                            put(pk, have);
+                        }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {   // rare: more than 16 outliers of one strip inside one stage
+                        const int cnt = __shfl_sync(0xffffffffu, e0 - b0, h * 16);
+                        if (cnt > 16) {
+                            const int bb = __shfl_sync(0xffffffffu, b0, h * 16);
+                            for (int i = 16; i < cnt; ++i) {
+                                const uint32_t pk = pack((uint32_t)(h * 16), __ldg(p.entries + bb + i), (uint32_t)__ldg(p.ovals + bb + i));
+                                put(pk, (pk >> 23) == (uint32_t)lane && (int)((pk >> 22) & 1u) == j);
+                            }
+                        }
+                    }
+                    if (j == 0) {   // the A stage must have been read by the MMAs of its previous use
+                        if (st >= AS && !mbar_wait_warp<40>(done_bar_of(st - AS), done_par_of(st - AS), s_abort)) { ok = false; break; }
+                        tcgen05_fence_after();
+                    }
+                    tmem_st_32x32b_x32(taddr + (uint32_t)(j * (GM_BK / 2)), o);
                 }
             }
-            // the A stage must have been read by the MMAs of its previous use
-            if (around > 0 && !mbar_wait_warp<40>(mma_done(ph), (around - 1) & 1, s_abort)) { ok = false; break; }
-            tcgen05_fence_after();
-            tmem_st_32x32b_x32(taddr, o);
+            if (!ok) break;
             tmem_st_wait();
             tcgen05_fence_before();
-            mbar_arrive(ready_bar(ph));
+            mbar_arrive(ready_bar(st % GM_PH));
             ent0 = ent1; val0 = val1; ent1 = ent2; val1 = val2;
             b0 = b1; e0 = e1; b1 = b2; e1 = e2;
         }
@@ -472,11 +513,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
 
         // epilogue: TMEM lane = output feature, column = token.  The accumulators go through shared
         // memory (the rings are idle by now) so that y is written in 16-byte pieces along a token row.
-        if (dwi >= GM_EPI_WARPS) {
-            // only the first eight dequantizer warps drain the accumulator
-        } else if (mbar_wait_warp<200>(accfull_bar, 0, s_abort)) {
+        if (mbar_wait_warp<200>(accfull_bar, 0, s_abort)) {
             tcgen05_fence_after();
-            const int half = (warp - GM_CTRL_WARPS) >> 2;   // two warps share a quarter: columns [0,128) and [128,256)
+            const int part = (warp - GM_CTRL_WARPS) >> 2;   // four warps share a TMEM lane quarter: 32-column chunks part, part + 4, ..
             const int nl = q * 32 + lane;                   // feature inside the tile
             const int n = n0 + nl;
             const float bv = (p.bias && n < p.n_rows) ? __half2float(__ushort_as_half(__ldg(p.bias + n))) : 0.f;
@@ -485,7 +524,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             const bool partial = p.splits > 1;
             unsigned char *stage = base_ptr + OFF_B;
             const int st_bytes = partial ? (GM_BM + 4) * 4 : (GM_BM + 8) * 2;   // row stride; pads keep banks apart
-            for (int c = half; c < BN / 32; c += 2) {
+            for (int c = part; c < BN / 32; c += 4) {
                 if (m0 + c * 32 >= p.m) break;  // warp-uniform: no tokens left in this tile
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
@@ -504,7 +543,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             }
             // all eight epilogue warps have staged their part
             asm volatile("bar.sync 1, %0;" ::"n"(GM_EPI_WARPS * 32) : "memory");
-            const int et = tid - GM_CTRL_WARPS * 32;         // 0..255
+            const int et = tid - GM_CTRL_WARPS * 32;         // 0..511
             const int rows_left = min(BN, p.m - m0);
             if (partial) {
                 // fp32 partial tile -> partials[z][m][n], 16 bytes (4 features) per thread and store
