@@ -204,6 +204,17 @@ def test_gemm_small_batches_and_k_slices(m, n, k, cuda_device):
     assert torch.equal(bits(y), bits(y2))  # slices are added in a fixed order
 
 
+@pytest.mark.parametrize("n,k,bs,m", [(256, 192, 64, 40), (128, 64, 64, 300), (300, 320, 32, 17), (512, 1088, 64, 130),
+                                      (130, 448, 64, 257)])
+def test_gemm_odd_k_tile_counts_and_block_sizes(n, k, bs, m, cuda_device):
+    # an odd number of 64-column k-tiles leaves the last pipeline stage half full; block sizes below 64 take the
+    # scales from global memory instead of the staged copy
+    dtype = torch.float16 if m % 2 else torch.bfloat16
+    o, x, b, ref = _linear_case(n, k, m, dtype, 900 + n + k, bias=True, bs=bs)
+    y = _run_linear(o, x, b, cuda_device, "gemm")
+    assert rel_max_err(y, ref) < LINEAR_TOL, f"{n}x{k} bs={bs} m={m}"
+
+
 def test_gemm_llama_prefill_shape(cuda_device):
     # 2048 tokens against 4096 x 4096; the reference product is evaluated on the GPU in fp32
     # from the oracle's dequantized weight (the CPU oracle's fp64 loop would take minutes here)
