@@ -124,8 +124,9 @@ ATLAS_API int atlas_dequantize(const int8_t *codes, int64_t n_codes, const void 
  *
  *   tiles            atlas_tiles_bytes(n_rows, n_cols) bytes; code + 128 as
  *                    uint8 (outlier positions hold 128, i.e. code 0), ordered
- *                    [row/128][col/64][(row%128)/16][(row%16)/8][(row%8)*4 +
- *                    (col%64)/16][col%16]; rows padded to a multiple of 128
+ *                    [row/128][col/64][row%128][col%64] (every 128-row x
+ *                    64-column tile is a contiguous 8 KB matrix of 64-byte
+ *                    rows); rows padded to a multiple of 128
  *   scales_tiled     atlas_tiles_bytes / block_size fp16: the scales ordered
  *                    [row/128][block][row%128] (0 for padding rows)
  *   outlier_row_ptr  n_rows + 1 int32: CSR row starts into the canonical
@@ -158,18 +159,22 @@ ATLAS_API int atlas_repack(const int8_t *codes, int64_t n_codes, const void *out
  * that a kernel sets non-zero if one of its bounded waits ran out; the library
  * never clears it.
  *
- * atlas_qlinear_gemv: decode shapes, any m >= 1 (rows are processed in groups
- * of up to 32; intended for m <= 32).  HBM-bound: streams the tiles once per
- * group through per-warp shared-memory rings, dequantises in registers and
- * adds the outlier products in the same launch.  Launched with programmatic
- * dependent launch: only weights are read before the stream's earlier work
- * has completed.
+ * atlas_qlinear_gemv: decode shapes, any m >= 1 (intended for m <= 16).  HBM-
+ * bound: up to 16 rows are served 8 at a time by a kernel that gives each CTA
+ * one 16-row strip of the weight, streams its codes with 16-byte loads,
+ * dequantises in registers and adds the outlier products in the same launch
+ * (more rows, or activations that are not 16-byte aligned, go in groups of up
+ * to 32 through a slower kernel with per-warp shared-memory rings).  Launched
+ * with programmatic dependent launch: only weights are read before the
+ * stream's earlier work has completed.
  *
- * atlas_qlinear_gemm: batches above 8 rows (any m >= 1 accepted).  Stages
- * tiles through shared memory, dequantises to fp16 operand tiles and multiplies
- * with tcgen05 into TMEM accumulators; the token tile is 32, 64, 128 or 256
- * wide by m, and for decode-sized batches K is sliced over CTAs with the
- * fp32 partial tiles added in slice order by a second kernel (deterministic).
+ * atlas_qlinear_gemm: larger batches (any m >= 1 accepted).  The code tiles
+ * come in by TMA, are dequantised by 16 warps straight into tensor memory as
+ * the fp16 A operand of tcgen05.mma (the activations are the B operand, from
+ * shared memory; fp32 accumulators in tensor memory); the token tile is 32,
+ * 64, 128 or 256 wide by m, and for decode-sized batches K is sliced over CTAs
+ * with the fp32 partial tiles added in slice order by a second kernel
+ * (deterministic).
  * `workspace` must hold atlas_qlinear_gemm_workspace_bytes(m, n_rows, n_cols)
  * bytes, 256-byte aligned.
  */
