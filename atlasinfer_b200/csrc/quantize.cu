@@ -342,7 +342,7 @@ struct FastConsts {
 };
 
 template <int EPT>
-__global__ void __launch_bounds__(QT_THREADS, (EPT <= 16 ? 4 : 2)) quantize_fast_kernel(QuantParams p, FastConsts fc) {
+__global__ void __launch_bounds__(QT_THREADS, (EPT <= 16 ? 5 : 2)) quantize_fast_kernel(QuantParams p, FastConsts fc) {
     constexpr int BS = EPT * 8;
     constexpr int TILE_BLOCKS = QT_TILE / BS;
     // Blocks are padded (16 bytes of values, 8 bytes of codes) so that the four blocks a warp works
@@ -730,7 +730,7 @@ int atlas_quantize(const void *w, int64_t numel, int block_size, double z_thresh
     rc = device_info(di);
     if (rc) return rc;
     const bool fast = block_size == 32 || block_size == 64 || block_size == 128 || block_size == 256;
-    const int per_sm = fast ? (block_size == 256 ? 2 : 4) : di.quant_ctas_per_sm;   // resident CTAs of the fast kernels
+    const int per_sm = fast ? (block_size == 256 ? 2 : 5) : di.quant_ctas_per_sm;   // resident CTAs of the fast kernels
     const int64_t max_ctas = (int64_t)di.sms * per_sm;
     const int grid = (int)(p.num_tiles < max_ctas ? p.num_tiles : max_ctas);
     if (fast) {

@@ -317,6 +317,45 @@ def measure_quantize(steps, warmup):
     return nbytes * steps / secs / 1e9
 
 
+def measure_quantize_kernel(steps, warmup):
+    """The quantize kernel alone, through the C ABI with caller-owned buffers and no host synchronisation
+    (quantize_tensor adds allocations, a device-to-host read of the two stream lengths and two trims)."""
+    from atlasinfer_b200 import _capi
+    L = _capi.load()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(5)
+    ws = [synth_weight(n, k, gen) for n, k in ((11008, 4096), (4096, 11008), (4096, 4096), (11008, 4096))]
+    bufs, nbytes = [], 0
+    for w in ws:
+        flat = w.reshape(-1)
+        n = flat.numel()
+        cap = n // 8 + 1024
+        b = dict(flat=flat, n=n, cap=cap, codes=torch.empty(n, dtype=torch.int8, device=dev),
+                 ovals=torch.empty(cap, dtype=torch.float16, device=dev), oidx=torch.empty(cap, dtype=torch.int64, device=dev),
+                 scales=torch.empty(n // BLOCK, dtype=torch.float16, device=dev),
+                 counts=torch.zeros(4, dtype=torch.int64, device=dev))
+        b["ws_bytes"] = int(L.atlas_quantize_workspace_bytes(n, BLOCK))
+        b["ws"] = torch.empty(b["ws_bytes"], dtype=torch.uint8, device=dev)
+        bufs.append(b)
+    stream = _capi.stream_ptr(dev)
+
+    def one():
+        for b in bufs:
+            rc = L.atlas_quantize(b["flat"].data_ptr(), b["n"], BLOCK, 3.0, b["codes"].data_ptr(), b["ovals"].data_ptr(),
+                                  b["oidx"].data_ptr(), b["cap"], b["scales"].data_ptr(), b["counts"].data_ptr(),
+                                  b["ws"].data_ptr(), b["ws_bytes"], stream)
+            _capi.check(rc, "atlas_quantize")
+
+    one()
+    torch.cuda.synchronize()
+    for b in bufs:
+        n_codes, n_out, timed_out, _ = b["counts"].tolist()
+        assert not timed_out and n_codes + n_out == b["n"]
+        nbytes += 2 * b["n"] + n_codes + (b["n"] // BLOCK) * 2 + n_out * 10
+    secs = time_steps(one, steps, warmup)
+    return nbytes * steps / secs / 1e9
+
+
 def measure_tp70b(rank, world, steps, warmup, barrier):
     """Config 5: Llama-3-70B-shaped decode, batch 32, column-parallel over `world` ranks.
 
@@ -535,6 +574,7 @@ def run_ours(args, rank, world, local_rank):
         try:
             extra["prefill_gemm_tflops"] = measure_gemm(max(2, args.steps // 4), 3)
             extra["quantize_gbs"] = measure_quantize(max(2, args.steps // 4), 3)
+            extra["quantize_kernel_gbs"] = measure_quantize_kernel(max(2, args.steps // 4), 3)
         except Exception as e:  # noqa: BLE001 - secondary figures must not lose the headline line
             extra["error"] = repr(e)
 
@@ -599,8 +639,12 @@ def main():
         return
     if args.only:
         torch.cuda.set_device(local_rank)
-        fn = measure_gemm if args.only == "gemm" else measure_quantize
-        print(json.dumps({args.only: fn(args.steps, args.warmup)}), flush=True)
+        if args.only == "gemm":
+            out = {"gemm": measure_gemm(args.steps, args.warmup)}
+        else:
+            out = {"quantize": measure_quantize(args.steps, args.warmup),
+                   "quantize_kernel": measure_quantize_kernel(args.steps, args.warmup)}
+        print(json.dumps(out), flush=True)
         return
     run_ours(args, rank, world, local_rank)
 
