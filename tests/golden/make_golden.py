@@ -115,4 +115,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("ATLASINFER_REFERENCE"):
+        sys.exit("usage: make_golden.py <path to an AtlasInfer checkout>  (or set ATLASINFER_REFERENCE)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["ATLASINFER_REFERENCE"])
