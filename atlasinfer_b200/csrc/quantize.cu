@@ -569,52 +569,66 @@ __global__ void __launch_bounds__(QT_THREADS, (EPT <= 16 ? 5 : 2)) quantize_fast
                     p.counts[1] = total_out;
                 }
             }
-        }
-        __syncthreads();
-
-        // ---- phase B: compact the codes in shared memory, outliers straight out --------
-        const long long tile_prefix = s_tile_prefix;
-        const int64_t code_base = tile_base - tile_prefix;  // where this tile's codes start
-        const int shift = p.out_aligned ? (int)(code_base & 15) : 0;
-        for (int i = tid * 4; i < tile_elems; i += QT_THREADS * 4) {
-            const uint32_t word = s_mask[i >> 5];
-            const uint32_t m4 = (word >> (i & 31)) & 0xfu;
-            int before = (int)s_wordpre[i >> 5] + __popc(word & ((1u << (i & 31)) - 1u));
-            const uint32_t c4 = *reinterpret_cast<const uint32_t *>(s_dense + (i / BS) * DSTRIDE + (i % BS));
-            const int dst = shift + i - before;
-            if (m4 == 0u && (dst & 3) == 0) {
-                *reinterpret_cast<uint32_t *>(s_codes + dst) = c4;
-            } else {
+        } else {
+            // ---- meanwhile, warps 1..7 compact the codes in shared memory (needs no prefix) ----------
+            for (int i = (tid - 32) * 4; i < tile_elems; i += (QT_THREADS - 32) * 4) {
+                const uint32_t word = s_mask[i >> 5];
+                const uint32_t m4 = (word >> (i & 31)) & 0xfu;
+                const int before = (int)s_wordpre[i >> 5] + __popc(word & ((1u << (i & 31)) - 1u));
+                const uint32_t c4 = *reinterpret_cast<const uint32_t *>(s_dense + (i / BS) * DSTRIDE + (i % BS));
+                int dst = i - before;
+                if (m4 == 0u && (dst & 3) == 0) {
+                    *reinterpret_cast<uint32_t *>(s_codes + dst) = c4;
+                } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if ((m4 >> e) & 1u) {
-                        const long long pos = tile_prefix + before;
-                        if (pos < p.ocap) {
-                            p.ovals[pos] = xref(i + e);
-                            p.oidx[pos] = tile_base + i + e;
-                        }
-                        before++;
-                    } else {
-                        s_codes[shift + i + e - before] = (uint8_t)(c4 >> (8 * e));
-                    }
+                    for (int e = 0; e < 4; ++e)
+                        if (!((m4 >> e) & 1u)) s_codes[dst++] = (uint8_t)(c4 >> (8 * e));
                 }
             }
         }
         __syncthreads();
 
-        // ---- copy the compacted codes out: 16-byte stores inside, bytes at the ragged ends --
+        // ---- with the prefix: outliers straight out, one mask word per thread ------------------------
+        const long long tile_prefix = s_tile_prefix;
+        const int64_t code_base = tile_base - tile_prefix;  // where this tile's codes start
+        const int shift = p.out_aligned ? (int)(code_base & 15) : 0;
+        {
+            uint32_t word = s_mask[tid];   // QT_WORDS == QT_THREADS
+            long long pos = tile_prefix + s_wordpre[tid];
+            while (word) {
+                const int e = tid * 32 + __ffs(word) - 1;
+                word &= word - 1;
+                if (pos < p.ocap) {
+                    p.ovals[pos] = xref(e);
+                    p.oidx[pos] = tile_base + e;
+                }
+                ++pos;
+            }
+        }
+
+        // ---- copy the compacted codes out: 16-byte stores to aligned global addresses, the shared-memory side is
+        // read at whatever byte offset the tile's start in the code stream leaves (five words and a funnel shift)
         {
             const int total = tile_elems - s_tile_total;  // code bytes of this tile
             const int end = shift + total;
             int8_t *gdst = p.codes + (code_base - shift);  // 16-byte aligned when out_aligned
             const int nchunks = (end + 15) >> 4;
+            const uint32_t *s32 = reinterpret_cast<const uint32_t *>(s_codes);
             for (int c = tid; c < nchunks; c += QT_THREADS) {
                 const int lo = c << 4;
                 if (p.out_aligned && lo >= shift && lo + 16 <= end) {
-                    *reinterpret_cast<uint4 *>(gdst + lo) = *reinterpret_cast<const uint4 *>(s_codes + lo);
+                    const int o = lo - shift;
+                    const int wi = o >> 2, r = (o & 3) * 8;
+                    const uint32_t w0 = s32[wi], w1 = s32[wi + 1], w2 = s32[wi + 2], w3 = s32[wi + 3], w4 = s32[wi + 4];
+                    uint4 v;
+                    v.x = __funnelshift_r(w0, w1, r);
+                    v.y = __funnelshift_r(w1, w2, r);
+                    v.z = __funnelshift_r(w2, w3, r);
+                    v.w = __funnelshift_r(w3, w4, r);
+                    *reinterpret_cast<uint4 *>(gdst + lo) = v;
                 } else {
                     const int a = max(lo, shift), z = min(lo + 16, end);
-                    for (int q = a; q < z; ++q) gdst[q] = (int8_t)s_codes[q];
+                    for (int q = a; q < z; ++q) gdst[q] = (int8_t)s_codes[q - shift];
                 }
             }
             const int64_t block0 = tile_base / BS;
