@@ -22,8 +22,23 @@ EXPORTS = (
     "atlas_version", "atlas_last_error", "atlas_status_string",
     "atlas_quantize_workspace_bytes", "atlas_quantize", "atlas_quantize_noalloc", "atlas_dequantize",
     "atlas_tiles_bytes", "atlas_repack", "atlas_qlinear_gemv",
+    "atlas_qlinear_stream_workspace_bytes", "atlas_qlinear_stream", "atlas_qlinear_stream_gather",
+    "atlas_peer_wait", "atlas_peer_alloc", "atlas_peer_free", "atlas_peer_export", "atlas_peer_import",
+    "atlas_peer_release",
     "atlas_qlinear_gemm_workspace_bytes", "atlas_qlinear_gemm",
 )
+
+MAX_PEERS = 8
+PEER_HANDLE_BYTES = 64
+
+
+class PeerGather(ctypes.Structure):
+    """``AtlasPeerGather`` of include/atlas_b200.h."""
+
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32),
+                ("y_dst", ctypes.c_void_p * MAX_PEERS), ("flags_dst", ctypes.c_void_p * MAX_PEERS),
+                ("state", ctypes.c_void_p), ("wait_flags", ctypes.c_void_p), ("poll_limit", ctypes.c_int64)]
+
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -66,6 +81,24 @@ def load() -> ctypes.CDLL:
     lin = [vp, i32, i64, i64, vp, vp, vp, vp, vp, i64, i64, i32, vp, vp, i64]
     L.atlas_qlinear_gemv.restype = i32
     L.atlas_qlinear_gemv.argtypes = lin + [vp, vp]
+    L.atlas_qlinear_stream_workspace_bytes.restype = sz
+    L.atlas_qlinear_stream_workspace_bytes.argtypes = [i64]
+    L.atlas_qlinear_stream.restype = i32
+    L.atlas_qlinear_stream.argtypes = lin + [vp, sz, vp, vp]
+    L.atlas_qlinear_stream_gather.restype = i32
+    L.atlas_qlinear_stream_gather.argtypes = lin[:13] + [i64, vp, sz, vp, vp, ctypes.POINTER(PeerGather)]
+    L.atlas_peer_wait.restype = i32
+    L.atlas_peer_wait.argtypes = [vp, i32, vp, i64, vp, vp]
+    L.atlas_peer_alloc.restype = i32
+    L.atlas_peer_alloc.argtypes = [sz, ctypes.POINTER(vp)]
+    L.atlas_peer_free.restype = i32
+    L.atlas_peer_free.argtypes = [vp]
+    L.atlas_peer_export.restype = i32
+    L.atlas_peer_export.argtypes = [vp, ctypes.c_char_p]
+    L.atlas_peer_import.restype = i32
+    L.atlas_peer_import.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    L.atlas_peer_release.restype = i32
+    L.atlas_peer_release.argtypes = [vp]
     L.atlas_qlinear_gemm_workspace_bytes.restype = sz
     L.atlas_qlinear_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     L.atlas_qlinear_gemm.restype = i32

@@ -18,7 +18,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libatlas_b200.so")
 
-SOURCES = ["capi.cu", "quantize.cu", "dequant_repack.cu", "gemv.cu", "gemm.cu"]
+SOURCES = ["capi.cu", "quantize.cu", "dequant_repack.cu", "gemv.cu", "stream.cu", "peer.cu", "gemm.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -76,6 +76,7 @@ struct QuantParams {
     unsigned long long *status;
     int in_aligned;   // x is 16-byte aligned
     int out_aligned;  // codes is 16-byte aligned
+    int tile;         // elements per tile: the largest multiple of the block size <= QT_TILE
 };
 
 __global__ void __launch_bounds__(QT_THREADS) quantize_kernel(QuantParams p) {
@@ -103,8 +104,8 @@ __global__ void __launch_bounds__(QT_THREADS) quantize_kernel(QuantParams p) {
         __syncthreads();
         const int64_t tile = s_tile;
         if (tile >= p.num_tiles) break;
-        const int64_t tile_base = tile * QT_TILE;
-        const int tile_elems = (int)min((int64_t)QT_TILE, p.padded - tile_base);
+        const int64_t tile_base = tile * p.tile;   // tiles hold whole blocks
+        const int tile_elems = (int)min((int64_t)p.tile, p.padded - tile_base);
         const int tile_real = (int)max((int64_t)0, min((int64_t)tile_elems, p.numel - tile_base));
         const int tile_blocks = tile_elems / bs;
 
@@ -688,9 +689,10 @@ int device_info(DeviceInfo &out) {
 extern "C" {
 
 size_t atlas_quantize_workspace_bytes(int64_t numel, int block_size) {
-    if (numel <= 0 || block_size <= 0) return 16;
+    if (numel <= 0 || block_size <= 0 || block_size > atlas::QT_TILE) return 16;
     const int64_t padded = atlas::ceil_div_i64(numel, block_size) * block_size;
-    const int64_t tiles = atlas::ceil_div_i64(padded, atlas::QT_TILE);
+    const int64_t tile = (atlas::QT_TILE / block_size) * block_size;   // a tile holds whole blocks
+    const int64_t tiles = atlas::ceil_div_i64(padded, tile);
     return (size_t)(16 + 8 * tiles);
 }
 
@@ -724,7 +726,8 @@ int atlas_quantize(const void *w, int64_t numel, int block_size, double z_thresh
     p.numel = numel;
     p.n_blocks = ceil_div_i64(numel, block_size);
     p.padded = p.n_blocks * block_size;
-    p.num_tiles = ceil_div_i64(p.padded, QT_TILE);
+    p.tile = (QT_TILE / block_size) * block_size;
+    p.num_tiles = ceil_div_i64(p.padded, p.tile);
     p.bs = block_size;
     p.thr_h = __half_as_ushort(__float2half_rn((float)z_threshold));
     p.codes = codes;
@@ -815,6 +818,11 @@ extern "C" int atlas_quantize_noalloc(const void *w, int64_t numel, int block_si
                     "atlas_quantize_noalloc: %lld padded elements exceed the static scratch limit of %lld; "
                     "use atlas_quantize with a caller-provided workspace",
                     (long long)padded, (long long)ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS);
+    // block sizes that do not divide the 8192-element tile use slightly smaller tiles, hence more status words
+    ATLAS_RETURN_IF(block_size <= QT_TILE && atlas_quantize_workspace_bytes(numel, block_size) > sizeof(g_quantize_scratch),
+                    ATLAS_ERR_CAPACITY,
+                    "atlas_quantize_noalloc: %lld elements in blocks of %d exceed the static scratch limit; "
+                    "use atlas_quantize with a caller-provided workspace", (long long)numel, block_size);
     void *scratch = nullptr;
     int rc = check_device();
     if (rc) return rc;

@@ -56,37 +56,64 @@ class QuantizedTensor(NamedTuple):
         return total + (128 if include_overhead else 0)
 
 
-def _quantize_on_device(flat: torch.Tensor, block_size: int, z_threshold: float):
-    """Run the quantize kernel on a flat fp16 CUDA tensor; returns the four streams."""
+def _launch_quantize(flat: torch.Tensor, block_size: int, z_threshold: float, counts: torch.Tensor, capacity: int):
+    """Enqueue the quantize kernel for a flat fp16 CUDA tensor; nothing is read back here."""
     L = _capi.load()
     dev = flat.device
     numel = flat.numel()
     n_blocks = (numel + block_size - 1) // block_size
     padded = n_blocks * block_size
+    ws_bytes = int(L.atlas_quantize_workspace_bytes(numel, block_size))
     with torch.cuda.device(dev):
         codes = torch.empty(padded, dtype=torch.int8, device=dev)
         scales = torch.empty(n_blocks, dtype=torch.float16, device=dev)
-        counts = torch.empty(4, dtype=torch.int64, device=dev)
-        ws_bytes = int(L.atlas_quantize_workspace_bytes(numel, block_size))
         workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        # |z| > t bounds the outliers of a block by (block_size - 1) / t^2; start with an
-        # eighth of the tensor and retry with full capacity in the rare case that is short
-        capacity = min(padded, padded // 8 + 1024)
-        while True:
-            ovals = torch.empty(capacity, dtype=torch.float16, device=dev)
-            oidx = torch.empty(capacity, dtype=torch.int64, device=dev)
-            status = L.atlas_quantize(
-                flat.data_ptr(), numel, block_size, float(z_threshold), codes.data_ptr(),
-                _capi.ptr(ovals), _capi.ptr(oidx), capacity, scales.data_ptr(), counts.data_ptr(),
-                workspace.data_ptr(), ws_bytes, _capi.stream_ptr(dev))
-            _capi.check(status, "atlas_quantize")
-            n_codes, n_out, timed_out, _ = counts.tolist()  # synchronises
+        ovals = torch.empty(capacity, dtype=torch.float16, device=dev)
+        oidx = torch.empty(capacity, dtype=torch.int64, device=dev)
+        status = L.atlas_quantize(
+            flat.data_ptr(), numel, block_size, float(z_threshold), codes.data_ptr(),
+            _capi.ptr(ovals), _capi.ptr(oidx), capacity, scales.data_ptr(), counts.data_ptr(),
+            workspace.data_ptr(), ws_bytes, _capi.stream_ptr(dev))
+    _capi.check(status, "atlas_quantize")
+    return dict(flat=flat, codes=codes, scales=scales, ovals=ovals, oidx=oidx, workspace=workspace,
+                capacity=capacity, padded=padded)
+
+
+def _first_capacity(padded: int) -> int:
+    # |z| > t bounds the outliers of a block by (block_size - 1) / t^2, but weight-like data has well under
+    # 1 %: start with 1/32 of the tensor and retry with full capacity in the rare case that is short
+    return min(padded, padded // 32 + 1024)
+
+
+def _quantize_many_on_device(flats, block_size: int, z_threshold: float):
+    """Quantize several flat fp16 CUDA tensors (one device): all kernels are enqueued first, the stream
+    lengths of all of them come back in one device-to-host copy.  Returns the four streams per tensor."""
+    dev = flats[0].device
+    with torch.cuda.device(dev):
+        counts = torch.empty((len(flats), 4), dtype=torch.int64, device=dev)
+    jobs = []
+    for i, flat in enumerate(flats):
+        padded = (flat.numel() + block_size - 1) // block_size * block_size
+        jobs.append(_launch_quantize(flat, block_size, z_threshold, counts[i], _first_capacity(padded)))
+    host = counts.cpu()   # the one synchronisation
+    out = []
+    for i, job in enumerate(jobs):
+        n_codes, n_out, timed_out, _ = (int(v) for v in host[i])
+        if timed_out:
+            raise _capi.AtlasError(_capi.ERR_TIMEOUT, "atlas_quantize: device-side wait timed out")
+        if n_out > job["capacity"]:   # rare: more outliers than the first buffer holds
+            job = _launch_quantize(job["flat"], block_size, z_threshold, counts[i], job["padded"])
+            n_codes, n_out, timed_out, _ = (int(v) for v in counts[i].cpu())
             if timed_out:
                 raise _capi.AtlasError(_capi.ERR_TIMEOUT, "atlas_quantize: device-side wait timed out")
-            if n_out <= capacity:
-                break
-            capacity = padded
-    return codes[:n_codes], ovals[:n_out].clone(), oidx[:n_out].clone(), scales
+        # codes: a view (the buffer is 0.3 % longer than the stream); outliers: copied out of their roomy buffers
+        out.append((job["codes"][:n_codes], job["ovals"][:n_out].clone(), job["oidx"][:n_out].clone(), job["scales"]))
+    return out
+
+
+def _quantize_on_device(flat: torch.Tensor, block_size: int, z_threshold: float):
+    """Run the quantize kernel on a flat fp16 CUDA tensor; returns the four streams."""
+    return _quantize_many_on_device([flat], block_size, z_threshold)[0]
 
 
 def quantize_tensor(
@@ -121,6 +148,39 @@ def quantize_tensor(
     if input_device != dev:
         codes, ovals, oidx, scales = (t.to(input_device) for t in (codes, ovals, oidx, scales))
     return QuantizedTensor(codes, ovals, oidx, scales, original_shape, block_size)
+
+
+def quantize_tensors(tensors, block_size: int = 128, z_threshold: float = 3.0):
+    """``[quantize_tensor(t, block_size, z_threshold) for t in tensors]`` with one host synchronisation.
+
+    The reference quantizes layer by layer (integration/model_modifier.py:117-131).  Here the kernels of all
+    tensors are enqueued back to back and the data-dependent stream lengths are read once for the whole
+    batch, so the GPU never idles between tensors.  Results are identical to the one-by-one calls and live
+    on each input's device."""
+    tensors = list(tensors)
+    results = [None] * len(tensors)
+    per_device = {}
+    for i, t in enumerate(tensors):
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"Input must be a PyTorch Tensor, got {type(t)}")
+        if t.dtype != torch.float16:
+            print(f"Warning: Input tensor was {t.dtype}, converting to FP16 for quantization.")
+            t = t.to(torch.float16)
+        if t.numel() == 0:
+            results[i] = quantize_tensor(t, block_size, z_threshold)
+            continue
+        dev = _capi.require_cuda(t.device)
+        flat = t.detach().reshape(-1).contiguous()
+        if flat.device != dev:
+            flat = flat.to(dev, non_blocking=True)
+        per_device.setdefault(dev, []).append((i, flat, t.device, t.shape))
+    for dev, items in per_device.items():
+        streams = _quantize_many_on_device([f for _, f, _, _ in items], int(block_size), float(z_threshold))
+        for (i, _, in_dev, shape), (codes, ovals, oidx, scales) in zip(items, streams):
+            if in_dev != dev:
+                codes, ovals, oidx, scales = (x.to(in_dev) for x in (codes, ovals, oidx, scales))
+            results[i] = QuantizedTensor(codes, ovals, oidx, scales, shape, block_size)
+    return results
 
 
 # --- dequantization cache (reference :153-154): id(quant_data) -> fp16 tensor.  Each entry also

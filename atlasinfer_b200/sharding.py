@@ -86,10 +86,15 @@ def gather_columns(y_local: torch.Tensor, group: Optional[dist.ProcessGroup] = N
         dist.all_gather_into_tensor(out, flat, group=group)  # rank r's rows land at [r*M, (r+1)*M)
         out = out.view(world, flat.shape[0], flat.shape[1]).transpose(0, 1)
         return out.reshape(*lead, world * flat.shape[1])
-    parts: List[torch.Tensor] = [
-        torch.empty(tuple(lead) + (int(s),), dtype=y_local.dtype, device=y_local.device) for s in sizes]
-    dist.all_gather(parts, y_local, group=group)
-    return torch.cat(parts, dim=-1)
+    # shards of different widths: collectives want equal sizes, so every rank pads its shard to the widest one
+    flat = y_local.reshape(-1, y_local.shape[-1])
+    widest = max(int(s) for s in sizes)
+    padded = flat if flat.shape[1] == widest else torch.nn.functional.pad(flat, (0, widest - flat.shape[1]))
+    out = torch.empty((world * flat.shape[0], widest), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(out, padded.contiguous(), group=group)
+    out = out.view(world, flat.shape[0], widest)
+    parts: List[torch.Tensor] = [out[r, :, :int(s)] for r, s in enumerate(sizes)]
+    return torch.cat(parts, dim=-1).reshape(*lead, sum(int(s) for s in sizes))
 
 
 class ColumnParallelQuantizedLinear(nn.Module):

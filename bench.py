@@ -7,25 +7,30 @@ Headline metric (BASELINE.json): decode dequant-GEMV HBM GB/s on the
 Llama-2-7B-shaped quantized linears (32 layers x q/k/v/o 4096x4096, gate/up
 11008x4096, down 4096x11008), batch 1, bf16 activations.  One step = one pass
 over all 224 linears (6.5 G weights, 6.7 GB of quantized data: every step
-streams far more than the 126 MB L2, so nothing is served from cache).
+streams far more than the 126 MB L2, so nothing is served from cache).  The
+linears are `QuantizedLinear` modules built through the public API
+(quantize_tensors -> QuantizedLinear -> fuse_linears for q/k/v and gate/up ->
+offload_canonical), so a step is 4 launches per layer, 128 in all.
 
   value     algorithmic bytes of a step / device time, inputs resident in HBM,
-            the step replayed from a CUDA graph (one launch per linear)
-  e2e       the same pass through QuantizedLinear.forward with host activations:
-            every step copies the activations from pinned host memory to the
-            device, replays a CUDA graph captured from the 224 module calls and
-            copies all 224 outputs back to pinned host memory, inside the timed
-            region (`extra.e2e_eager_gbs`: the same with copy-in, call and
-            copy-out issued per linear from Python, no graph)
-  extra     the other two figures BASELINE.json names (prefill GEMM TFLOP/s,
-            quantize GB/s), GEMV at batch 4 and 16 and, with --gpus > 1, the
-            70B-shaped column-parallel decode (batch 32, NCCL all-gather)
+            the step (the module calls) replayed from a CUDA graph
+  e2e       the same pass with host activations: every step copies the
+            activations from pinned host memory to the device, replays the
+            graph and copies all 224 outputs back to pinned host memory, inside
+            the timed region
+  extra     the same pass without fusing (224 launches), batch 4 / 16 / 32,
+            prefill GEMM TFLOP/s, quantize GB/s, the OPT-1.3B-architecture model
+            end to end (quantize seconds, greedy decode tokens/s) and the
+            70B-shaped column-parallel decode (batch 32) at this N, with the
+            NCCL all-gather and with the kernels' own peer stores
 
-With --gpus N > 1 every rank runs the same pass on its own GPU (replicas, no
+With --gpus N > 1 every rank runs the headline pass on its own GPU (replicas, no
 collective: the path shards by independent tensors) and `value` is the sum over
-ranks / max time over ranks ("weak").  --impl reference times the reference's
-forward on the host cores (rank 0 only): torch CPU F.linear on the cached fp16
-weight, with the first-call dequantization (CPU oracle port) reported beside it.
+ranks / max time over ranks ("weak"); the sharded 70B-shaped decode is the
+config that communicates, reported per N in `extra.tp70b_decode`.
+--impl reference times the reference's forward on the host cores (rank 0 only):
+torch CPU F.linear on the cached fp16 weight, with the first-call
+dequantization (CPU oracle port) reported beside it.
 """
 from __future__ import annotations
 
@@ -50,6 +55,7 @@ LLAMA7B_LINEARS = [("q_proj", 4096, 4096), ("k_proj", 4096, 4096), ("v_proj", 40
 LLAMA70B_LINEARS = [("q_proj", 8192, 8192), ("k_proj", 1024, 8192), ("v_proj", 1024, 8192),
                     ("o_proj", 8192, 8192), ("gate_proj", 28672, 8192), ("up_proj", 28672, 8192),
                     ("down_proj", 8192, 28672)]
+FUSED = (("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj"))
 BLOCK = 128
 NO_GRAPH = False
 
@@ -82,47 +88,41 @@ def linear_bytes(n, k, n_out, m):
     return (n * k - n_out) + (n * k // BLOCK) * 2 + n_out * 6 + m * k * 2 + m * n * 2
 
 
-class Linear:
-    """Device-resident kernel image of one quantized linear (canonical code stream dropped)."""
+class Layer:
+    """One decoder layer's quantized linears as the public API builds them."""
 
-    def __init__(self, w, keep_module=False):
+    def __init__(self, linears, gen, sigma, fuse, rows_slice=None):
         import atlasinfer_b200 as ab
-        from atlasinfer_b200.integration import atlas_wrappers as aw
-        q = ab.quantize_tensor(w)
-        self.n, self.k = w.shape
-        self.n_out = q.fp16_outliers.numel()
-        lay = aw.build_kernel_layout(q)
-        torch.cuda.current_stream().synchronize()
-        # the kernels read only the repacked layout; the canonical streams are not needed afterwards
-        slim = ab.QuantizedTensor(torch.empty(0, dtype=torch.int8, device=w.device),
-                                  torch.empty(0, dtype=torch.float16, device=w.device),
-                                  torch.empty(0, dtype=torch.long, device=w.device),
-                                  torch.empty(0, dtype=torch.float16, device=w.device),
-                                  q.original_shape, q.block_size)
-        self.q = slim
-        self.layout = lay._replace(source=slim)
-        self.module = None
-        if keep_module:
-            self.module = ab.QuantizedLinear(slim, None)
-            self.module._kernel_layout = self.layout
-
-    def forward(self, x, force=None):
-        from atlasinfer_b200.integration import atlas_wrappers as aw
-        return aw.quantized_linear_forward(x, self.layout, None, force)
-
-
-def build_model(linears, layers, gen, sigma, rows_slice=None, keep_module=False):
-    """`layers` x the given linears; rows_slice=(rank, world) keeps this rank's output rows."""
-    out = []
-    for _ in range(layers):
-        for name, n, k in linears:
+        ws = []
+        for _, n, k in linears:
             if rows_slice is not None:
-                r, wsz = rows_slice
-                n = n // wsz
-            w = synth_weight(n, k, gen, sigma)
-            out.append((name, Linear(w, keep_module)))
-            del w
-    return out
+                n = n // rows_slice[1]
+            ws.append(synth_weight(n, k, gen, sigma))
+        qs = ab.quantize_tensors(ws)                          # one host synchronisation for the layer
+        del ws
+        self.mods = {name: ab.QuantizedLinear(q, None) for (name, _, _), q in zip(linears, qs)}
+        self.stats = {name: (int(q.original_shape[0]), int(q.original_shape[1]), q.fp16_outliers.numel())
+                      for (name, _, _), q in zip(linears, qs)}
+        self.groups = []
+        if fuse:
+            for names in FUSED:
+                self.groups.append(ab.fuse_linears([self.mods[n] for n in names]))
+        dev = qs[0].fp8_data.device
+        for g in self.groups:
+            g.build(dev)
+        for mod in self.mods.values():
+            mod.offload_canonical()        # the GPU keeps the kernel layout only (~1.03 B per weight)
+        # the order a decoder layer calls them in; members of a fused group are called back to back with one input
+        self.calls = list(self.mods.items())
+        fused_names = {n for names in FUSED for n in names} if fuse else set()
+        self.launches = len(self.groups) + sum(1 for n in self.mods if n not in fused_names)
+
+    def nbytes(self, m):
+        return sum(linear_bytes(n, k, no, m) for n, k, no in self.stats.values())
+
+
+def build_model(linears, layers, gen, sigma, fuse=True, rows_slice=None):
+    return [Layer(linears, gen, sigma, fuse, rows_slice) for _ in range(layers)]
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -204,64 +204,58 @@ def capture_graph(fn):
     return g
 
 
+def allmax(v, world, dev):
+    if world == 1:
+        return v
+    import torch.distributed as dist
+    t = torch.tensor([v], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 # ----------------------------------------------------------------------------- measurements
+def decode_pass(model, xs, outs):
+    """One decode step over `model`: every linear called through QuantizedLinear.forward with its input."""
+    outs.clear()
+    for layer in model:
+        for name, mod in layer.calls:
+            outs.append(mod(xs[mod.original_shape[1]]))
+
+
 def measure_gemv(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16):
     """(bytes per step, seconds for `steps`, launches per step) of a graph-replayed decode pass."""
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev).manual_seed(7 + m)
-    xs = {k: torch.randn(m, k, generator=gen, device=dev).to(dtype) for k in {l.k for _, l in model}}
+    xs = {k: torch.randn(m, k, generator=gen, device=dev).to(dtype) for k in {s[1] for l in model for s in l.stats.values()}}
     outs = []
-
-    def one_pass():
-        outs.clear()
-        for _, lin in model:
-            outs.append(lin.forward(xs[lin.k]))   # the library's own dispatch for this batch size
-
+    fn = lambda: decode_pass(model, xs, outs)  # noqa: E731
     if NO_GRAPH:
-        secs = time_steps(one_pass, steps, warmup, barrier)
+        secs = time_steps(fn, steps, warmup, barrier)
     else:
-        graph = capture_graph(one_pass)
+        graph = capture_graph(fn)
         secs = time_steps(graph.replay, steps, warmup, barrier)
-    nbytes = sum(linear_bytes(l.n, l.k, l.n_out, m) for _, l in model)
-    return nbytes, secs, len(model)
+    return sum(l.nbytes(m) for l in model), secs, sum(l.launches for l in model)
 
 
-def measure_e2e(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16, eager=False):
-    """The decode pass through the public module API (`QuantizedLinear.forward`) with host-resident activations.
-
-    Every step copies the step's activations from pinned host memory to the device, runs the 224 module
-    calls and copies all 224 outputs back to pinned host memory, then waits for them.  Default: the module
-    calls are captured once in a CUDA graph (the way a serving loop drives a decode step) that reads static
-    input tensors; `eager=True` instead issues copy-in, call, copy-out per linear from Python."""
+def measure_e2e(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16):
+    """The decode pass with host-resident activations: per step the activations go from pinned host memory to the
+    device, a CUDA graph captured from the module calls is replayed, all outputs go back to pinned host memory
+    and the host waits for them."""
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator().manual_seed(11)
-    hx = {k: torch.randn(m, k, generator=gen).to(dtype).pin_memory() for k in {l.k for _, l in model}}
-    nbytes = sum(linear_bytes(l.n, l.k, l.n_out, m) for _, l in model)
-    if eager:
-        hy = {n: torch.empty(m, n, dtype=dtype).pin_memory() for n in {l.n for _, l in model}}
-
-        def one_pass():
-            for _, lin in model:
-                x = hx[lin.k].to(dev, non_blocking=True)
-                y = lin.module(x)
-                hy[lin.n].copy_(y, non_blocking=True)
-            torch.cuda.current_stream().synchronize()  # the caller holds y on the host
-
-        secs = time_steps(one_pass, steps, warmup, barrier)
-        return nbytes, secs, sum(m * l.k * 2 for _, l in model), sum(m * l.n * 2 for _, l in model)
-
+    dims = {s[1] for l in model for s in l.stats.values()}
+    hx = {k: torch.randn(m, k, generator=gen).to(dtype).pin_memory() for k in dims}
     dx = {k: torch.empty(m, k, dtype=dtype, device=dev) for k in hx}
-    total_out = sum(m * l.n for _, l in model)
-    hy = torch.empty(total_out, dtype=dtype).pin_memory()
     for k in hx:
         dx[k].copy_(hx[k])
-    for _, lin in model[:8]:
-        lin.module(dx[lin.k])           # warm the call path before capture
+    outs = []
+    decode_pass(model, dx, outs)          # warm the call path before capture
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        outs = [lin.module(dx[lin.k]) for _, lin in model]
+        decode_pass(model, dx, outs)
         flat = torch.cat([o.reshape(-1) for o in outs])
+    hy = torch.empty(flat.numel(), dtype=dtype).pin_memory()
 
     def one_pass():
         for k in hx:
@@ -271,55 +265,53 @@ def measure_e2e(model, m, steps, warmup, barrier=None, dtype=torch.bfloat16, eag
         torch.cuda.current_stream().synchronize()  # the caller holds every output on the host
 
     secs = time_steps(one_pass, steps, warmup, barrier)
-    return nbytes, secs, sum(m * k * 2 for k in hx), total_out * 2
+    return sum(l.nbytes(m) for l in model), secs, sum(m * k * 2 for k in hx), flat.numel() * 2
 
 
 def measure_gemm(steps, warmup):
     """Prefill GEMM TFLOP/s: 2048 tokens against 11008x4096 and 4096x4096 (config 4)."""
+    import atlasinfer_b200 as ab
+    from atlasinfer_b200.integration import atlas_wrappers as aw
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev).manual_seed(99)
     res = {}
     for n, k in ((11008, 4096), (4096, 4096)):
         # several distinct weights so that consecutive calls do not re-read one from L2
         reps = 4
-        lins = [Linear(synth_weight(n, k, gen)) for _ in range(reps)]
+        lays = [aw.build_kernel_layout(q) for q in ab.quantize_tensors([synth_weight(n, k, gen) for _ in range(reps)])]
         x = torch.randn(2048, k, generator=gen, device=dev).to(torch.bfloat16)
         ch = torch.randperm(k, generator=gen, device=dev)[: max(1, round(0.005 * k))]
         x[:, ch] *= 20
 
         def one():
-            for l in lins:
-                l.forward(x, "gemm")
+            for lay in lays:
+                aw.quantized_linear_forward(x, lay, None, "gemm")
 
         secs = time_steps(one, steps, warmup)
         res[f"{n}x{k}"] = 2.0 * 2048 * n * k * reps * steps / secs / 1e12
-        del lins
+        del lays
     return res
 
 
+def quantize_bytes(numel, n_out):
+    return 2 * numel + (numel - n_out) + (numel // BLOCK) * 2 + n_out * 10
+
+
 def measure_quantize(steps, warmup):
-    """Quantize GB/s on the 7B shapes: algorithmic bytes = 2 B read + codes + scales + 10 B per outlier."""
+    """Quantize GB/s on the 7B shapes through the public API (quantize_tensors: one synchronisation per batch);
+    algorithmic bytes = 2 B read + codes + scales + 10 B per outlier."""
     import atlasinfer_b200 as ab
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev).manual_seed(5)
     ws = [synth_weight(n, k, gen) for n, k in ((11008, 4096), (4096, 11008), (4096, 4096), (11008, 4096))]
-    nbytes = 0
-    for w in ws:
-        q = ab.quantize_tensor(w)
-        n_out = q.fp16_outliers.numel()
-        nbytes += 2 * w.numel() + (w.numel() - n_out) + (w.numel() // BLOCK) * 2 + n_out * 10
-
-    def one():
-        for w in ws:
-            ab.quantize_tensor(w)
-
-    secs = time_steps(one, steps, warmup)
-    return nbytes * steps / secs / 1e9
+    nbytes = sum(quantize_bytes(w.numel(), q.fp16_outliers.numel()) for w, q in zip(ws, ab.quantize_tensors(ws)))
+    secs = time_steps(lambda: ab.quantize_tensors(ws), steps, warmup)
+    one = time_steps(lambda: [ab.quantize_tensor(w) for w in ws], steps, warmup)
+    return nbytes * steps / secs / 1e9, nbytes * steps / one / 1e9
 
 
 def measure_quantize_kernel(steps, warmup):
-    """The quantize kernel alone, through the C ABI with caller-owned buffers and no host synchronisation
-    (quantize_tensor adds allocations, a device-to-host read of the two stream lengths and two trims)."""
+    """The quantize kernel alone, through the C ABI with caller-owned buffers and no host synchronisation."""
     from atlasinfer_b200 import _capi
     L = _capi.load()
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -351,98 +343,167 @@ def measure_quantize_kernel(steps, warmup):
     for b in bufs:
         n_codes, n_out, timed_out, _ = b["counts"].tolist()
         assert not timed_out and n_codes + n_out == b["n"]
-        nbytes += 2 * b["n"] + n_codes + (b["n"] // BLOCK) * 2 + n_out * 10
+        nbytes += quantize_bytes(b["n"], n_out)
     secs = time_steps(one, steps, warmup)
     return nbytes * steps / secs / 1e9
+
+
+def measure_opt13b():
+    """Config 2: a random-init OPT-1.3B-architecture model quantized end to end on the GPU through the applier
+    (fused q/k/v), then greedy decode of 128 new tokens from 128 seeded prompt ids (HF generate, eager)."""
+    import atlasinfer_b200 as ab
+    from transformers import OPTConfig, OPTForCausalLM
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = OPTConfig(vocab_size=50272, hidden_size=2048, ffn_dim=8192, num_hidden_layers=24, num_attention_heads=32,
+                    max_position_embeddings=2048, word_embed_proj_dim=2048)
+    with torch.device(dev):
+        model = OPTForCausalLM(cfg).half().eval()
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    n_weights = 0
+    for name, mod in model.named_modules():
+        if isinstance(mod, torch.nn.Linear) and "lm_head" not in name:
+            mod.weight.data.copy_(synth_weight(*mod.weight.shape, gen))
+            n_weights += mod.weight.numel()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ab.apply_atlas_quantization_to_model(model, "opt", {"block_size": BLOCK, "z_threshold": 3.0},
+                                         keep_on_device=True, fuse=True, offload_canonical=True, verbose=False)
+    torch.cuda.synchronize()
+    t_quant = time.perf_counter() - t0
+    ids = torch.randint(0, 50272, (1, 128), generator=torch.Generator().manual_seed(9)).to(dev)
+    with torch.no_grad():
+        model.generate(ids, max_new_tokens=4, min_new_tokens=4, do_sample=False)       # warm-up
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = model.generate(ids, max_new_tokens=128, min_new_tokens=128, do_sample=False)
+        torch.cuda.synchronize()
+        t_gen = time.perf_counter() - t0
+    assert out.shape[1] == 256
+    res = dict(linears=144, weights=n_weights, quantize_s=t_quant, quantize_gweights_per_s=n_weights / t_quant / 1e9,
+               decode_tokens_per_s=128 / t_gen, decode="HF generate, eager, batch 1, 128 prompt + 128 new tokens")
+    del model
+    torch.cuda.empty_cache()
+    return res
 
 
 def measure_tp70b(rank, world, steps, warmup, barrier):
     """Config 5: Llama-3-70B-shaped decode, batch 32, column-parallel over `world` ranks.
 
-    Every rank owns rows [r*N/g, (r+1)*N/g) of each linear (8 distinct layers, cycled ten times to
-    stand for the 80 layers; one layer's shards already exceed L2 together with the gathers) and
-    all-gathers its [32, N/g] output shard over NCCL.  Returns ms per token with and without the
-    gathers, and the aggregate algorithmic GB/s of the weight streaming.
-    """
+    Every rank owns rows [r*N/g, (r+1)*N/g) of each linear (8 distinct layers, cycled ten times to stand for the
+    80 layers; one layer's shards already exceed L2), q/k/v and gate/up fused into one launch each, and the
+    [32, N/g] output shards are all-gathered after every launch: by NCCL (`nccl_allgather`), or by the ranks'
+    own peer stores into symmetric buffers followed by a flag exchange (`peer_stores`, see
+    atlasinfer_b200/peer.py).  Returns ms per token for each, the weight-streaming-only time and the aggregate
+    algorithmic GB/s."""
     import torch.distributed as dist
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev).manual_seed(777 + rank)
     layers, reps, m = 8, 10, 32
-    model = build_model(LLAMA70B_LINEARS, layers, gen, 0.015, rows_slice=(rank, world))
-    xs = {k: torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16) for k in {l.k for _, l in model}}
-    gathered = {l.n: torch.empty(world * m, l.n, dtype=torch.bfloat16, device=dev) for _, l in model}
+    model = build_model(LLAMA70B_LINEARS, layers, gen, 0.015, fuse=True, rows_slice=(rank, world))
+    xs = {k: torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16) for k in (8192, 28672)}
+    # what a layer launches: (kernel layout of the launch, output rows it produces on this rank)
+    from atlasinfer_b200.integration import atlas_wrappers as aw
+    launches = []
+    for layer in model:
+        by_first = {g.members[0]: g for g in layer.groups}
+        for names in (("q_proj", "k_proj", "v_proj"), ("o_proj",), ("gate_proj", "up_proj"), ("down_proj",)):
+            first = layer.mods[names[0]]
+            lay = by_first[first].layout if first in by_first else first._kernel_layout
+            launches.append((lay, lay.n_rows))
+    widths = sorted({w for _, w in launches})
+    gathered = {w: torch.empty(world * m, w, dtype=torch.bfloat16, device=dev) for w in widths}
+    out = {}
 
     def one_pass(gather):
         for _ in range(reps):
-            for _, lin in model:
-                y = lin.forward(xs[lin.k])
+            for lay, width in launches:
+                y = aw.quantized_linear_forward(xs[lay.n_cols], lay, None)
                 if gather and world > 1:
-                    dist.all_gather_into_tensor(gathered[lin.n], y)
+                    dist.all_gather_into_tensor(gathered[width], y)
 
-    out = {}
-    for name, gather in (("with_allgather", True), ("gemv_only", False)):
+    modes = [("gemv_only", False)] + ([("nccl_allgather", True)] if world > 1 else [])
+    for name, gather in modes:
         fn = lambda: one_pass(gather)  # noqa: E731
         try:
             graph = capture_graph(fn)
-            run = graph.replay
-            mode = "graph"
+            run, mode = graph.replay, "graph"
         except Exception:  # noqa: BLE001 - capture of the collective not available: launch directly
             torch.cuda.synchronize()
             run, mode = fn, "eager"
-        secs = time_steps(run, steps, warmup, barrier)
-        t = torch.tensor([secs], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        out[name] = dict(ms_per_token=float(t.item()) / steps * 1e3, launch=mode)
-    nbytes = sum(linear_bytes(l.n, l.k, l.n_out, m) for _, l in model) * reps
+        secs = allmax(time_steps(run, steps, warmup, barrier), world, dev)
+        out[name] = dict(ms_per_token=secs / steps * 1e3, launch=mode)
+    if world > 1:
+        try:
+            out["peer_stores"] = measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, world, dev)
+        except Exception as e:  # noqa: BLE001 - keep the NCCL figures
+            out["peer_stores"] = dict(error=repr(e))
+    nbytes = sum(l.nbytes(m) for l in model) * reps
     tot = torch.tensor([float(nbytes)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(tot)
-    out["aggregate_gbs_with_allgather"] = float(tot.item()) / (out["with_allgather"]["ms_per_token"] * 1e-3) / 1e9
-    out["aggregate_gbs_gemv_only"] = float(tot.item()) / (out["gemv_only"]["ms_per_token"] * 1e-3) / 1e9
-    out["config"] = "llama3-70b-shaped linears, 80 layers (8 distinct x 10), batch 32 bf16, rows sharded over %d ranks" % world
+    total = float(tot.item())
+    pk = peaks()
+    for name in list(out):
+        if "ms_per_token" in out[name]:
+            gbs = total / (out[name]["ms_per_token"] * 1e-3) / 1e9
+            out[name]["aggregate_gbs"] = gbs
+            out[name]["frac_of_n_x_hbm"] = gbs / (world * pk["hbm"])
+    out["launches_per_token"] = len(launches) * reps
+    out["config"] = ("llama3-70b-shaped linears, 80 layers (8 distinct x 10), batch 32 bf16, q/k/v and gate/up fused, "
+                     "rows sharded over %d ranks" % world)
     del model
     torch.cuda.empty_cache()
     return out
 
 
+def measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, world, dev):
+    """The column-parallel decode pass with the kernels' own peer stores instead of NCCL: one gathered buffer per
+    launch kind of a layer, every launch waiting (bounded) for the previous launch's arrivals from all ranks."""
+    from atlasinfer_b200 import peer
+    from atlasinfer_b200.integration import atlas_wrappers as aw
+    per_layer = 4
+    arena = peer.PeerArena(sum(m * lay.n_rows * world * 2 + 256 for lay, _ in launches[:per_layer]) + 4096, dev)
+    try:
+        kinds = [peer.GatheredLinear(arena, lay, m, torch.bfloat16) for lay, _ in launches[:per_layer]]
+
+        def one_pass():
+            for _ in range(reps):
+                for i, (lay, _) in enumerate(launches):
+                    g = kinds[i % per_layer]
+                    g.layout = lay              # same shapes in every layer: one gathered buffer per kind, own weights
+                    g(xs[lay.n_cols], wait=True)
+
+        one_pass()
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            one_pass()
+        secs = allmax(time_steps(graph.replay, steps, warmup, barrier), world, dev)
+        aw.check_status(dev)
+        return dict(ms_per_token=secs / steps * 1e3, launch="graph")
+    finally:
+        arena.close()
+
+
 def measure_quantize_sharded(rank, world, steps, warmup, barrier):
     """Whole-model quantization sharded by layer: every rank quantizes whole layers of its own
     (one 70B-shaped layer per step here), no collective.  Aggregate algorithmic GB/s."""
-    import torch.distributed as dist
     import atlasinfer_b200 as ab
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev).manual_seed(4242 + rank)
     ws = [synth_weight(n, k, gen, 0.015) for _, n, k in LLAMA70B_LINEARS]
-    nbytes = 0
-    for w in ws:
-        q = ab.quantize_tensor(w)
-        n_out = q.fp16_outliers.numel()
-        nbytes += 2 * w.numel() + (w.numel() - n_out) + (w.numel() // BLOCK) * 2 + n_out * 10
-
-    def one():
-        for w in ws:
-            ab.quantize_tensor(w)
-
-    secs = time_steps(one, steps, warmup, barrier)
-    t = torch.tensor([secs], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return world * nbytes * steps / float(t.item()) / 1e9
+    nbytes = sum(quantize_bytes(w.numel(), q.fp16_outliers.numel()) for w, q in zip(ws, ab.quantize_tensors(ws)))
+    secs = allmax(time_steps(lambda: ab.quantize_tensors(ws), steps, warmup, barrier), world, dev)
+    return world * nbytes * steps / secs / 1e9
 
 
-def cpu_linear_pass(linears, m):
-    """The reference's forward on the host cores over `linears` [(n, k)].
+CPU_SAMPLE = [(4096, 4096), (11008, 4096), (4096, 11008)]
 
-    integration/atlas_wrappers.py:54-67 calls dequantize_tensor (adaptive_quantizer.py:156, which keeps the
-    fp16 reconstruction in a cache keyed by the weight object) and then F.linear: the first call of a
-    layer pays the dequantization, every later call multiplies by the cached fp16 weight.  Both are
-    timed: the steady state with torch's own CPU F.linear on fp16 tensors (the very call the reference
-    makes; fp32 if this torch build has no fp16 CPU matmul), the first call with the oracle's
-    dequantizer in front of it.  Returns (algorithmic bytes, steady-state seconds, first-call seconds);
-    the bytes are those of the quantized format, so the figure is comparable with the GPU lines.
-    Weights are quantized (untimed) by the oracle first."""
-    import torch.nn.functional as F
+
+def cpu_prepare(linears, m):
+    """Quantized weights and activations of the CPU arm (oracle quantizer; untimed)."""
     from oracle import atlas_oracle as O
     gen = torch.Generator().manual_seed(3)
     prepared = []
@@ -453,6 +514,21 @@ def cpu_linear_pass(linears, m):
         q = O.quantize(w.half())
         x = torch.randn(m, k, generator=gen).half()
         prepared.append((q, x, linear_bytes(n, k, q.fp16_outliers.numel(), m)))
+    return prepared
+
+
+def cpu_linear_pass(prepared, reps=5):
+    """The reference's forward on the host cores over prepared (weight, activation) pairs.
+
+    integration/atlas_wrappers.py:54-67 calls dequantize_tensor (adaptive_quantizer.py:156, which keeps the
+    fp16 reconstruction in a cache keyed by the weight object) and then F.linear: the first call of a
+    layer pays the dequantization, every later call multiplies by the cached fp16 weight.  Both are
+    timed: the steady state with torch's own CPU F.linear on fp16 tensors (the very call the reference
+    makes; fp32 if this torch build has no fp16 CPU matmul), the first call with the oracle's
+    dequantizer in front of it.  Returns (algorithmic bytes, steady-state seconds per pass, first-call seconds);
+    the bytes are those of the quantized format, so the figure is comparable with the GPU lines."""
+    import torch.nn.functional as F
+    from oracle import atlas_oracle as O
     t0 = time.perf_counter()
     cached = [O.dequantize(q) for q, _, _ in prepared]          # the reference's per-weight cache
     t_dequant = time.perf_counter() - t0
@@ -462,13 +538,23 @@ def cpu_linear_pass(linears, m):
     except RuntimeError:                                         # no fp16 matmul on this CPU build
         cached = [c.float() for c in cached]
         xs = [x.float() for _, x, _ in prepared]
-    reps = 5
     t0 = time.perf_counter()
     for _ in range(reps):
         for x, wd in zip(xs, cached):
             F.linear(x, wd)
     t_steady = (time.perf_counter() - t0) / reps
     return sum(b for _, _, b in prepared), t_steady, t_steady + t_dequant
+
+
+def host_threads():
+    """Use every host core: under torch.distributed.run the environment pins OMP to one thread."""
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        pass
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
 
 
 # ----------------------------------------------------------------------------- arms
@@ -478,42 +564,39 @@ def run_reference(args, rank, world):
         return
     from oracle import atlas_oracle as O
     O.build()
-    sample = [(4096, 4096), (11008, 4096), (4096, 11008)]
+    cores = host_threads()
+    prepared = cpu_prepare(CPU_SAMPLE, 1)        # quantized once, outside the step loop
     for _ in range(max(0, min(args.warmup, 1))):
-        cpu_linear_pass(sample[:1], 1)
+        cpu_linear_pass(prepared[:1], 1)
     t_all, t_first, b_all = 0.0, 0.0, 0
     for _ in range(args.steps):
-        b, t, tf = cpu_linear_pass(sample, 1)
+        b, t, tf = cpu_linear_pass(prepared, 1)
         t_all += t
         t_first += tf
         b_all += b
     val = b_all / t_all / 1e9
-    cores = torch.get_num_threads()
-    desc = ("per step: q_proj 4096x4096 + gate_proj 11008x4096 + down_proj 4096x11008 at batch 1; steady state of "
-            "the reference's forward = torch CPU F.linear on the cached fp16 weight; the first call of a layer "
-            f"(dequantize_tensor, CPU oracle port, OpenMP, then F.linear) runs at {b_all / t_first / 1e9:.3f} GB/s")
+    desc = ("bounded sample of the workload per step: q_proj 4096x4096 + gate_proj 11008x4096 + down_proj 4096x11008 "
+            "at batch 1; steady state of the reference's forward = torch CPU F.linear on the cached fp16 weight; the "
+            f"first call of a layer (dequantize_tensor, CPU oracle port, OpenMP, then F.linear) runs at "
+            f"{b_all / t_first / 1e9:.3f} GB/s")
     line = dict(
         impl="reference", metric="dequant_gemv_hbm_gbs", value=val, unit="GB/s", n_gpus=args.gpus,
         steps=args.steps, warmup=args.warmup, ms_per_step=t_all / args.steps * 1e3, higher_is_better=True,
-        scaling="weak", vs_baseline=None, dtype="fp16 weight rebuilt from int8 codes x fp16 scales (cached), torch CPU matmul",
-        data="synthetic", config=workload_config(1), gpu_launches=0,
+        scaling="weak", vs_baseline=None, dtype="int8 codes x fp16 scales -> fp16 MMA, fp32 accumulate",
+        data="synthetic", config=workload_config(1, args.layers), gpu_launches=0,
         cpu_baseline=dict(value=val, unit="GB/s", cores=cores, kind="port", sample=desc),
         e2e=dict(value=val, unit="GB/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
 
 
-NCU_DRAM_BYTES_PER_WEIGHT = 1.039   # dram__bytes_read.sum + dram__bytes_write.sum per weight of gemv_strip_kernel
+NCU_DRAM_BYTES_PER_WEIGHT = 1.039   # dram__bytes_read.sum + dram__bytes_write.sum per weight, from the ncu capture
 
 
-def weights_per_layer(linears):
-    return float(sum(n * k for _, n, k in linears))
-
-
-def workload_config(m):
+def workload_config(m, layers):
     return dict(workload="llama2-7b decode linears: 32 layers x (q,k,v,o 4096x4096; gate,up 11008x4096; "
                          "down 4096x11008), block 128, z 3.0, weights N(0,0.02)+0.1% outliers",
                 batch=m, activations="bf16 N(0,1)", l2="each step streams 6.7 GB of weights (>> 126 MB L2)",
-                launch="one kernel per linear, step replayed from a CUDA graph")
+                launch="q/k/v and gate/up fused: 4 kernels per layer, step replayed from a CUDA graph", layers=layers)
 
 
 def run_ours(args, rank, world, local_rank):
@@ -524,44 +607,43 @@ def run_ours(args, rank, world, local_rank):
     _capi.load()  # fail here, loudly, if the CUDA library is missing
     barrier = None
     if world > 1:
-        os.environ["NCCL_DEBUG"] = os.environ.get("ATLAS_NCCL_DEBUG", "WARN")  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
         barrier = dist.barrier
     pk = peaks()
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     t_setup = time.perf_counter()
-    model = build_model(LLAMA7B_LINEARS, args.layers, gen, 0.02, keep_module=True)
+    model = build_model(LLAMA7B_LINEARS, args.layers, gen, 0.02, fuse=not args.no_fuse)
     torch.cuda.synchronize()
     t_setup = time.perf_counter() - t_setup
+    resident = torch.cuda.memory_allocated(dev)
 
     sampler = ClockSampler(local_rank)
     sampler.start()
     nbytes, secs, launches = measure_gemv(model, 1, args.steps, args.warmup, barrier)
     clocks = sampler.stop()
     e_bytes, e_secs, h2d, d2h = measure_e2e(model, 1, args.steps, args.warmup, barrier)
-
-    def allmax(v):
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    secs, e_secs = allmax(secs), allmax(e_secs)
+    secs, e_secs = allmax(secs, world, dev), allmax(e_secs, world, dev)
     value = world * nbytes * args.steps / secs / 1e9
     e2e_value = world * e_bytes * args.steps / e_secs / 1e9
     per_gpu = value / world
+    n_weights = sum(n * k for l in model for n, k, _ in l.stats.values())
 
-    extra = {}
+    extra = dict(resident_bytes_per_weight=resident / n_weights)
+    half = max(2, args.steps // 2)
     if rank == 0 and not args.headline_only:
-        eb, es, _, _ = measure_e2e(model, 1, max(2, args.steps // 5), 2, eager=True)
-        extra["e2e_eager_gbs"] = eb * max(2, args.steps // 5) / es / 1e9   # copy-in, call, copy-out per linear from Python
-        for m in (4, 16):
-            b, s, _ = measure_gemv(model, m, max(2, args.steps // 2), 3)
-            extra[f"decode_m{m}_gbs"] = b * max(2, args.steps // 2) / s / 1e9
+        for m in (4, 16, 32):
+            b, s, _ = measure_gemv(model, m, half, 3)
+            extra[f"decode_m{m}_gbs"] = b * half / s / 1e9
     del model
     torch.cuda.empty_cache()
-    if world > 1 and not args.headline_only:
+    if rank == 0 and not args.headline_only and not args.no_fuse:
+        unfused = build_model(LLAMA7B_LINEARS, args.layers, torch.Generator(device=dev).manual_seed(99), 0.02, fuse=False)
+        b, s, ln = measure_gemv(unfused, 1, half, 3)
+        extra["unfused_gbs"] = b * half / s / 1e9
+        extra["unfused_launches_per_step"] = ln
+        del unfused
+        torch.cuda.empty_cache()
+    if not args.headline_only:
         try:
             tp = measure_tp70b(rank, world, max(2, args.steps // 5), 3, barrier)
             qs = measure_quantize_sharded(rank, world, 2, 1, barrier)
@@ -571,41 +653,47 @@ def run_ours(args, rank, world, local_rank):
         except Exception as e:  # noqa: BLE001 - keep the headline line
             extra["tp70b_error"] = repr(e)
     if rank == 0 and not args.headline_only:
-        try:
-            extra["prefill_gemm_tflops"] = measure_gemm(max(2, args.steps // 4), 3)
-            extra["quantize_gbs"] = measure_quantize(max(2, args.steps // 4), 3)
-            extra["quantize_kernel_gbs"] = measure_quantize_kernel(max(2, args.steps // 4), 3)
-        except Exception as e:  # noqa: BLE001 - secondary figures must not lose the headline line
-            extra["error"] = repr(e)
+        quarter = max(2, args.steps // 4)
+        for name, fn in (("prefill_gemm_tflops", lambda: measure_gemm(quarter, 3)),
+                         ("quantize_gbs", lambda: dict(zip(("batched", "one_by_one"), measure_quantize(quarter, 3)))),
+                         ("quantize_kernel_gbs", lambda: measure_quantize_kernel(quarter, 3)),
+                         ("opt_1p3b", measure_opt13b)):
+            try:
+                extra[name] = fn()
+            except Exception as e:  # noqa: BLE001 - secondary figures must not lose the headline line
+                extra[name + "_error"] = repr(e)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle import atlas_oracle as O
         O.build()
-        b, t, tf = cpu_linear_pass([(4096, 4096), (11008, 4096)], 1)
-        cpu = dict(value=b / t / 1e9, unit="GB/s", cores=torch.get_num_threads(), kind="port",
+        cores = host_threads()
+        b, t, tf = cpu_linear_pass(cpu_prepare(CPU_SAMPLE[:2], 1))
+        cpu = dict(value=b / t / 1e9, unit="GB/s", cores=cores, kind="port",
                    sample="q_proj 4096x4096 + gate_proj 11008x4096 at batch 1; steady state of the reference's "
                           "forward (torch CPU F.linear on the cached fp16 weight); with the first-call "
                           f"dequantization (CPU oracle port, OpenMP) in front: {b / tf / 1e9:.3f} GB/s")
 
     if rank == 0:
+        cfg = workload_config(1, args.layers)
+        if args.no_fuse:
+            cfg["launch"] = "one kernel per linear, step replayed from a CUDA graph"
         line = dict(
             metric="dequant_gemv_hbm_gbs", value=value, unit="GB/s", n_gpus=world, steps=args.steps,
             warmup=args.warmup, ms_per_step=secs / args.steps * 1e3, higher_is_better=True, scaling="weak",
             vs_baseline=None, dtype="int8 codes x fp16 scales -> fp16 MMA, fp32 accumulate", data="synthetic",
-            config=dict(workload_config(1), layers=args.layers), clocks=clocks,
+            config=cfg, clocks=clocks,
             e2e=dict(value=e2e_value, unit="GB/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                      method="per step: pinned-host activations -> device, CUDA-graph replay of the 224 "
                             "QuantizedLinear.forward calls, all 224 outputs -> pinned host, wait"),
             gpu_launches=launches * args.steps,
             roofline=dict(bound="hbm", achieved=per_gpu, peak=pk["hbm"], unit="GB/s", frac=per_gpu / pk["hbm"],
-                          # DRAM bytes per launch, averaged over the step's launches: ncu measured 17.43 MB for a
-                          # 4096x4096 linear and 46.82 MB for 4096x11008 (1.039 B per weight, equal to the
-                          # algorithmic bytes); the 11008x4096 launches are taken at the same bytes per weight
-                          traffic=NCU_DRAM_BYTES_PER_WEIGHT * weights_per_layer(LLAMA7B_LINEARS) / len(LLAMA7B_LINEARS),
+                          # DRAM bytes per launch from the ncu capture of the kernel (bytes per weight x the
+                          # weights an average launch of the step covers)
+                          traffic=NCU_DRAM_BYTES_PER_WEIGHT * n_weights / launches,
                           traffic_unit="bytes per launch", algorithmic_bytes_per_launch=nbytes / launches,
                           avg_launch_us=secs / args.steps / launches * 1e6,
-                          peak_source=pk["source"], kernel="gemv_strip_kernel",
+                          peak_source=pk["source"], kernel="qlinear_stream_kernel",
                           frac_of_nominal_8tbs=per_gpu / 8000.0),
             cpu_baseline=cpu, extra=extra, setup_s=t_setup)
         print(json.dumps(line), flush=True)
@@ -622,10 +710,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true", help="skip the secondary figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-fuse", action="store_true", help="one launch per linear (224 per step) instead of 4 per layer")
     ap.add_argument("--layers", type=int, default=LLAMA7B["layers"],
                     help="decoder layers in the pass (default: the full 32; smaller only for profiler captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch the pass directly instead of replaying a graph")
-    ap.add_argument("--only", default=None, choices=["gemm", "quantize"],
+    ap.add_argument("--only", default=None, choices=["gemm", "quantize", "opt13b", "tp70b"],
                     help="run just one of the secondary measurements and print it (for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -641,6 +730,20 @@ def main():
         torch.cuda.set_device(local_rank)
         if args.only == "gemm":
             out = {"gemm": measure_gemm(args.steps, args.warmup)}
+        elif args.only == "opt13b":
+            out = {"opt_1p3b": measure_opt13b()}
+        elif args.only == "tp70b":
+            barrier = None
+            if world > 1:
+                import torch.distributed as dist
+                dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+                barrier = dist.barrier
+            out = {"tp70b_decode": measure_tp70b(rank, world, args.steps, args.warmup, barrier)}
+            if world > 1:
+                dist.barrier()
+                dist.destroy_process_group()
+            if rank != 0:
+                return
         else:
             out = {"quantize": measure_quantize(args.steps, args.warmup),
                    "quantize_kernel": measure_quantize_kernel(args.steps, args.warmup)}

@@ -59,7 +59,8 @@ ATLAS_API const char *atlas_status_string(int status);
  * the reference's.
  *
  *   w              numel fp16 values
- *   block_size     multiple of 32, 32..512 (others: ATLAS_ERR_UNSUPPORTED)
+ *   block_size     multiple of 32, 32..512 (others: ATLAS_ERR_UNSUPPORTED);
+ *                  32 / 64 / 128 / 256 take the fast kernel
  *   z_threshold    as given to the reference; rounded to fp16 inside
  *   codes          capacity padded_numel int8  (compacted non-outlier codes)
  *   outlier_vals   capacity outlier_capacity fp16
@@ -84,18 +85,22 @@ ATLAS_API int atlas_quantize(const void *w, int64_t numel, int block_size, doubl
  * No counterpart in the reference.  Same computation and outputs as
  * atlas_quantize, but the look-back scratch lives in a device array inside the
  * library instead of a caller-provided workspace, and the call performs no
- * device or host allocation (it issues one cudaMemsetAsync and one kernel).
+ * device or host allocation (it issues two cudaMemsetAsync and one kernel).
  * Meant for hosts that must not allocate where they quantize: a fixed,
  * pre-reserved memory arena, a serving loop that forbids cudaMalloc after
  * start-up, a plug-in that does not own the allocator.
  *
  *  - limit: ceil(numel / block_size) * block_size <=
- *    ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS (64 Mi elements, e.g. 8192 x 8192);
+ *    ATLAS_QUANTIZE_NOALLOC_MAX_ELEMENTS (64 Mi elements, e.g. 8192 x 8192;
+ *    about 0.4 % fewer for block sizes that do not divide 8192);
  *    larger inputs return ATLAS_ERR_CAPACITY and must use atlas_quantize.
  *    The array (64 KB + 16 B) is held by every GPU context that loads the
  *    library, until the process exits.
  *  - the first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *    The address is cached per device ordinal for the life of the process: a
+ *    cudaDeviceReset() destroys the array it points to, so do not call this
+ *    entry point again on a device that was reset.
  *  - all calls on a device share the array: it is cleared on the stream at the
  *    start of every call, and two calls whose kernels may overlap on the GPU
  *    (different streams without ordering) race.  Serialise them.
@@ -183,6 +188,100 @@ ATLAS_API int atlas_qlinear_gemv(const void *x, int dtype, int64_t m, int64_t ld
                                  const uint32_t *outlier_entries, const void *outlier_vals_sorted,
                                  int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y,
                                  int64_t ldy, int32_t *status, void *stream);
+
+/* atlas_qlinear_stream: decode shapes, the weight read once for up to 32 rows
+ * of x per launch (more rows: one pass per 32).  One persistent CTA per SM; the
+ * 8 KB code tiles, taken row-tile-major, are cut into equal contiguous ranges,
+ * one per CTA, and stream through a shared-memory ring of bulk copies that the
+ * CTA starts filling before the stream's earlier work has completed
+ * (programmatic dependent launch; two consecutive launches are co-resident on
+ * an SM).  Row tiles whose K range is shared between CTAs are finished by the
+ * CTA that arrives last, which adds the fp32 partial tiles in CTA order
+ * (deterministic; no CTA waits for another).
+ *
+ * `workspace`: atlas_qlinear_stream_workspace_bytes(m) bytes, 16-byte aligned,
+ * ZERO-FILLED before its first use.  Every call leaves it zero-filled where it
+ * must be, so one workspace serves any number of calls of any shape that are
+ * ordered on one stream; calls that may overlap on the GPU need separate
+ * workspaces.  After a call that reported a timed-out wait through `status`,
+ * zero it again.
+ *
+ * Preconditions shared by the three linear entry points: the weight-side
+ * buffers (tiles, scales_tiled, outlier_*) are read before the stream's
+ * earlier work has completed, so they must be final before the kernel that
+ * precedes the call on the stream was launched (synchronise once after
+ * atlas_repack).  x, bias, y, workspace and status are only touched afterwards.
+ */
+ATLAS_API size_t atlas_qlinear_stream_workspace_bytes(int64_t m);
+ATLAS_API int atlas_qlinear_stream(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
+                                   const void *scales_tiled, const int32_t *outlier_chunk_ptr,
+                                   const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+                                   int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y,
+                                   int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
+                                   void *stream);
+
+/* ---- column-parallel linear with the gather fused into the kernel ---------------
+ * No counterpart in the reference (it is single-process; nothing to cite).
+ * For a weight sharded by output rows over `world` GPUs of one node, each rank
+ * computes its [m, n_rows] shard with atlas_qlinear_stream's kernel and stores
+ * it straight into every rank's gathered output (plain peer stores over
+ * NVLink; no TMA, no multicast), instead of writing y locally and calling an
+ * all-gather.  When its last CTA has finished, the rank publishes an arrival
+ * count into every rank's flag array; a consumer of the gathered buffer waits
+ * until all `world` flags have reached its own rank's count.  That wait is part
+ * of this kernel's prologue when `wait_flags` is given (its x is then a
+ * gathered buffer: it is read only after the wait, through L2), and is
+ * available on its own as atlas_peer_wait.  Every wait polls at most
+ * `poll_limit` times; when it runs out the kernel sets `status` and goes on.
+ *
+ *   world, rank   ranks sharing the weight (1..ATLAS_MAX_PEERS), this rank
+ *   y_dst[d]      address on rank d where element (row 0, first output
+ *                 feature of THIS rank) goes; row stride `ldy` elements
+ *                 (y_dst[rank] is local memory, the others are peer mappings)
+ *   flags_dst[d]  rank d's arrival flags (`world` x uint32); this rank writes
+ *                 entry [rank]
+ *   state         local, 2 x uint32, zero before first use: CTAs finished,
+ *                 gather launches completed (the arrival count)
+ *   wait_flags    local arrival flags to wait on before x is read, or NULL
+ *   poll_limit    polls per wait (each ~0.1 us)
+ * The peer mappings come from atlas_peer_alloc / _export / _import below (or
+ * any other inter-process mapping of plain device memory).
+ */
+#define ATLAS_MAX_PEERS 8
+typedef struct AtlasPeerGather {
+    int32_t world;
+    int32_t rank;
+    void *y_dst[ATLAS_MAX_PEERS];
+    uint32_t *flags_dst[ATLAS_MAX_PEERS];
+    uint32_t *state;
+    const uint32_t *wait_flags;
+    int64_t poll_limit;
+} AtlasPeerGather;
+
+ATLAS_API int atlas_qlinear_stream_gather(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
+                                          const void *scales_tiled, const int32_t *outlier_chunk_ptr,
+                                          const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+                                          int64_t n_rows, int64_t n_cols, int block_size, const void *bias,
+                                          int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
+                                          void *stream, const AtlasPeerGather *gather);
+
+/* Waits (one small kernel on `stream`) until all `world` entries of `flags`
+ * have reached the count in state[1]; sets *status non-zero if `poll_limit`
+ * polls were not enough.  For consumers of a gathered buffer that are not
+ * atlas kernels. */
+ATLAS_API int atlas_peer_wait(const uint32_t *flags, int world, const uint32_t *state, int64_t poll_limit,
+                              int32_t *status, void *stream);
+
+/* Device memory that other processes of the node can map: plain cudaMalloc
+ * memory (zero-filled), exported / imported as CUDA IPC handles (64 bytes).
+ * These four calls are the only ones in the library that own memory; it is
+ * freed by atlas_peer_free (imports by atlas_peer_release). */
+#define ATLAS_PEER_HANDLE_BYTES 64
+ATLAS_API int atlas_peer_alloc(size_t bytes, void **ptr);
+ATLAS_API int atlas_peer_free(void *ptr);
+ATLAS_API int atlas_peer_export(void *ptr, unsigned char *handle);
+ATLAS_API int atlas_peer_import(const unsigned char *handle, void **ptr);
+ATLAS_API int atlas_peer_release(void *ptr);
 
 ATLAS_API size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_rows, int64_t n_cols);
 ATLAS_API int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,

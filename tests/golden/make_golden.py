@@ -75,6 +75,12 @@ def cases():
     out["max_outliers_14"] = (x.to(torch.float16), 128, 3.0)
     # 3-D shape and odd trailing size
     out["shape_3x5x77"] = ((torch.randn(3, 5, 77, generator=g) * 0.1).to(torch.float16), 64, 3.0)
+    # block sizes that do not divide the CUDA quantizer's 8192-element tile, more than three tiles, ragged end;
+    # wide dynamic range so that the order of the fp32 block sum matters for these sizes too
+    for bs, n in ((96, 30001), (160, 26000), (384, 33333), (512, 20000)):
+        e = torch.randint(-12, 6, (n,), generator=g).float()
+        x = (torch.randn(n, generator=g) * torch.pow(2.0, e)).to(torch.float16)
+        out[f"odd_block_bs{bs}"] = (x, bs, 3.0)
     return out
 
 
@@ -90,6 +96,8 @@ def main(ref_root):
 
     torch.set_num_threads(1)
     for name, (w, bs, thr) in cases().items():
+        if os.path.exists(os.path.join(HERE, name + ".npz")) and not os.environ.get("ATLAS_GOLDEN_OVERWRITE"):
+            continue   # fixtures already in the tree stay as they are
         q = quantize_tensor(w, block_size=bs, z_threshold=thr)
         clear_dequantized_cache()
         d = dequantize_tensor(q, torch.device("cpu"))

@@ -41,12 +41,13 @@ def _worker(rank, world, port, uneven):
             return O.linear(x, w, self.bias).to(x.dtype)
         atlas_wrappers.QuantizedLinear.forward = oracle_forward
 
-        n = 80 if uneven else 64
+        n = 81 if uneven else 64   # 81 rows over 2 ranks: shards of 40 and 41 rows
         w = config_weights(n, 256, 11)
         bias = (torch.arange(n).float() * 0.01).half()
         q = QuantizedTensor(*O.quantize(w))
         layer = sharding.ColumnParallelQuantizedLinear.from_full(q, bias, rank, world, row_multiple=16 if not uneven else 48)
         assert sum(layer.shard_sizes) == n
+        assert (len(set(layer.shard_sizes)) > 1) == uneven   # the uneven case takes all_gather + cat
         x = torch.randn(3, 256, generator=torch.Generator().manual_seed(3)).half()
         y = layer(x)
         ref = O.linear(x, O.dequantize(q), bias).to(x.dtype)

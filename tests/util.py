@@ -62,22 +62,28 @@ def config_weights(rows, cols, seed, sigma=0.02):
     return w.to(torch.float16)
 
 
-def rel_max_err(y, ref, discount_output_rounding=True):
+def rel_max_err(y, ref, discount_output_rounding=None, report=None):
     """max|y - ref| / rms(ref): the linear outputs' tolerance metric (bound: 1e-2).
 
-    ``y`` is stored in fp16 or bf16, so even an exact kernel is off by up to half a unit in
-    the last place of that dtype (bf16: 2^-9 |y|, which alone reaches 1e-2 * rms at |y| ~ 5 rms).
-    That storage rounding is not the kernel's error: half an output ulp at each element is
-    subtracted before the maximum is taken.  The fp16 cases bound the same accumulators without
-    any meaningful discount (half an fp16 ulp is 2^-12 |y|).
+    fp16 outputs (the reference's dtype) are measured raw.  bf16 outputs are an extension (the
+    reference rejects bf16 activations): there even an exact kernel is off by up to half a unit in
+    the last place, 2^-9 |y|, which alone reaches 1e-2 * rms at |y| ~ 5 rms, so by default half a
+    bf16 ulp at each element is subtracted before the maximum is taken, and the raw figure is
+    printed beside the discounted one (pytest -s / -rP shows it).
     """
     out_dtype = y.dtype
+    if discount_output_rounding is None:
+        discount_output_rounding = out_dtype == torch.bfloat16
     y, ref = y.double().cpu(), ref.double().cpu()
     err = (y - ref).abs()
-    if discount_output_rounding and out_dtype in (torch.float16, torch.bfloat16):
-        mant = 7 if out_dtype == torch.bfloat16 else 10
-        mag = torch.maximum(y.abs(), ref.abs()).clamp(min=2.0 ** -14)
-        half_ulp = torch.pow(2.0, torch.floor(torch.log2(mag)) - mant - 1)
-        err = (err - half_ulp * 1.0001).clamp(min=0)
-    rms = ref.pow(2).mean().sqrt().item()
-    return err.max().item() / max(rms, 1e-30)
+    rms = max(ref.pow(2).mean().sqrt().item(), 1e-30)
+    raw = err.max().item() / rms
+    if not discount_output_rounding or out_dtype not in (torch.float16, torch.bfloat16):
+        return raw
+    mant = 7 if out_dtype == torch.bfloat16 else 10
+    mag = torch.maximum(y.abs(), ref.abs()).clamp(min=2.0 ** -14)
+    half_ulp = torch.pow(2.0, torch.floor(torch.log2(mag)) - mant - 1)
+    disc = (err - half_ulp * 1.0001).clamp(min=0).max().item() / rms
+    print(f"[tolerance] {report or ''} {str(out_dtype).replace('torch.', '')} output: raw max|err|/rms = {raw:.3e}, "
+          f"after removing half an output ulp = {disc:.3e}")
+    return disc
