@@ -30,13 +30,15 @@
 // as fp16 (bf16 is converted here, once per CTA and unit, not once per warp).
 // Eight consumer warps own one 16-row strip of the row tile each: 1 KB of codes
 // per unit from shared memory, dequantised in registers, four MMAs per 8 batch
-// rows.  A strip's outliers (sorted by column at repack time) are taken 16 at a
-// time as one more MMA, interleaved with the dense steps; their activations are
-// gathered from global memory (they stay in L1).
+// rows.  A strip's outliers (sorted by column at repack time) inside the columns
+// of a ring stage are taken 16 at a time as one more MMA per stage, with their
+// activations read from the stage in shared memory.
 //
 // Every wait is bounded; when one runs out the CTA sets the caller's status
 // word, stops waiting and runs to its end on whatever data it has.
 #include <cuda_bf16.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -45,6 +47,7 @@ namespace {
 
 constexpr int SK_CONSUMERS = 8;            // consumer warps = 16-row strips of a 128-row tile
 constexpr int SK_TILE_BYTES = 8192;        // 128 rows x 64 codes
+constexpr int SK_SKT = 2;                  // 64-column tiles per code stage (16 KB: what a warp can take to registers at once)
 constexpr int SK_SPIN_LIMIT = 1 << 20;     // polls per bounded wait
 constexpr int SK_MAX_GRID = 256;           // partial-tile slots in the workspace
 constexpr int SK_MAX_TILE_ROWS = 16384;    // tickets in the workspace (n_rows <= 2 Mi)
@@ -72,9 +75,13 @@ struct StreamParams {
     int blocks_per_row;  // n_cols / bs
     int tile_rows;       // ceil(n_rows / 128)
     long long units;     // tile_rows * k_tiles
+    int skt;             // 64-column tiles per ring stage (a stage never crosses a row tile)
     int scale_cap;       // bytes reserved for scales in a stage (multiple of 256)
-    int stage_stride;    // bytes per stage
-    int n_stages;
+    int x_row_bytes;     // skt * 128 + 16: stride of a batch row's activations in an activation stage
+    int stage_stride;    // bytes per code stage (codes + scales)
+    int n_stages;        // code stages
+    int x_stride;        // bytes per activation stage (m rows)
+    int x_stages;        // activation stages (a deeper ring than the codes': x cannot be requested before the wait)
     int x_vec_ok;        // x rows allow 16-byte loads
     unsigned int *tickets;   // [tile_rows], zero between launches
     float *partials;         // [grid][2][m][128] fp32
@@ -169,6 +176,17 @@ __device__ __forceinline__ void dequant4(uint32_t w, __half2 scale2, uint32_t &l
     hi = *reinterpret_cast<uint32_t *>(&hv);
 }
 
+// Four biased codes -> two half2 of the integer codes themselves (exact in fp16).
+__device__ __forceinline__ void codes4(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    const uint32_t l = __byte_perm(w, 0x64646464u, 0x5140);
+    const uint32_t h = __byte_perm(w, 0x64646464u, 0x5342);
+    const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));  // 1152
+    const __half2 lv = __hsub2(*reinterpret_cast<const __half2 *>(&l), bias);
+    const __half2 hv = __hsub2(*reinterpret_cast<const __half2 *>(&h), bias);
+    lo = *reinterpret_cast<const uint32_t *>(&lv);
+    hi = *reinterpret_cast<const uint32_t *>(&hv);
+}
+
 // Two bf16 (low, high half of v) -> two fp16, saturating at +-65504.
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
     uint32_t r;
@@ -181,15 +199,39 @@ __device__ __forceinline__ long long unit_begin(long long units, int grid, int c
 // MT: 8-column MMA tiles over the batch (m <= 8 * MT).
 template <int MT>
 struct StreamCfg {
-    static constexpr int XP_WARPS = 1;                                     // activation producers
-    static constexpr int FIRST_CONSUMER = 1 + XP_WARPS;
+    static constexpr int FIRST_CONSUMER = 2;                               // warp 0: codes, warp 1: activations
     static constexpr int THREADS = (FIRST_CONSUMER + SK_CONSUMERS) * 32;
-    static constexpr int X_BYTES = MT * 8 * 128;                           // fp16 [MT*8 rows][64]
     static constexpr int OUT_LD = MT * 8;                                  // floats per row of the staging tile
     static constexpr int OUT_BYTES = 128 * OUT_LD * 4;
 };
 
-template <int MT>
+// The CTA's units [u0, u1) cut into ring stages: runs of up to `skt` consecutive 64-column tiles of one row tile.
+// Every role walks the same sequence.
+struct StageWalk {
+    int r, kt, left, k_tiles, skt;
+    __device__ StageWalk(long long u0, int n_units, int k_tiles_, int skt_) : left(n_units), k_tiles(k_tiles_), skt(skt_) {
+        r = (int)(u0 / k_tiles_);
+        kt = (int)(u0 - (long long)r * k_tiles_);
+    }
+    // next stage: row tile, first tile column, tiles in the stage; false when the range is exhausted
+    __device__ bool next(int &sr, int &skt0, int &snk) {
+        if (left <= 0) return false;
+        sr = r;
+        skt0 = kt;
+        snk = min(skt, min(k_tiles - kt, left));
+        kt += snk;
+        left -= snk;
+        if (kt == k_tiles) { kt = 0; ++r; }
+        return true;
+    }
+};
+
+// POST: the MMAs take the integer codes themselves and a block's sum is multiplied by its scale afterwards (fp32),
+// which needs blocks that are whole 64-column tiles; otherwise every code is turned into the reference's fp16 weight
+// fp16(fp16(code) * scale) first.  Both are well inside the 1e-2 * rms tolerance of the linear's output; POST saves a
+// third of the dequantisation instructions and is the more accurate of the two (one rounding per block and row
+// instead of one per weight).
+template <int MT, bool POST>
 __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kernel(StreamParams p) {
     using C = StreamCfg<MT>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -199,16 +241,23 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cta = blockIdx.x, grid = gridDim.x;
     const int NS = p.n_stages;
-    // shared memory: stages | staging tile | barriers | flags
+    // shared memory: code stages | activation stages | zero row | staging tile | barriers | flags
+    const int XS = p.x_stages;
     const uint32_t smem0 = smem_u32(smem_raw);
-    float *s_out = reinterpret_cast<float *>(smem_raw + (size_t)NS * p.stage_stride);
-    const uint32_t bars = smem0 + (uint32_t)NS * p.stage_stride + C::OUT_BYTES;
-    volatile int *s_flags = reinterpret_cast<volatile int *>(smem_raw + (size_t)NS * p.stage_stride + C::OUT_BYTES + 16 * NS);
+    unsigned char *x_ring = smem_raw + (size_t)NS * p.stage_stride;
+    unsigned char *zero_row = x_ring + (size_t)XS * p.x_stride;
+    float *s_out = reinterpret_cast<float *>(zero_row + p.x_row_bytes);
+    unsigned char *bar_base = reinterpret_cast<unsigned char *>(s_out) + C::OUT_BYTES;
+    const uint32_t bars = smem_u32(bar_base);
+    volatile int *s_flags = reinterpret_cast<volatile int *>(bar_base + 16 * NS + 24 * XS);
     volatile int *s_abort = s_flags;        // [0] a bounded wait ran out somewhere in the CTA
     volatile int *s_ticket = s_flags + 1;   // [1] ticket drawn for the row tile being finished
-    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto full_bar = [&](int s) { return bars + 8u * s; };                       // codes and scales of a stage have landed
     auto empty_bar = [&](int s) { return bars + 8u * (NS + s); };
-    const uint32_t w_off = 0, sc_off = SK_TILE_BYTES, x_off = SK_TILE_BYTES + (uint32_t)p.scale_cap;
+    auto xraw_bar = [&](int s) { return bars + 8u * (2 * NS + s); };            // activation bytes have landed
+    auto xfull_bar = [&](int s) { return bars + 8u * (2 * NS + XS + s); };      // ... and are fp16
+    auto xempty_bar = [&](int s) { return bars + 8u * (2 * NS + 2 * XS + s); };
+    const uint32_t sc_off = (uint32_t)p.skt * SK_TILE_BYTES;
 
     const long long u0 = unit_begin(p.units, grid, cta), u1 = unit_begin(p.units, grid, cta + 1);
     const int n_units = (int)(u1 - u0);
@@ -216,43 +265,46 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
-            mbar_init(full_bar(s), 2);                 // the code producer (with its bytes) + one activation producer
+            mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), SK_CONSUMERS);
+        }
+        for (int s = 0; s < XS; ++s) {
+            mbar_init(xraw_bar(s), 1);
+            mbar_init(xfull_bar(s), 1);
+            mbar_init(xempty_bar(s), SK_CONSUMERS);
         }
         s_flags[0] = 0;
         s_flags[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // batch rows that do not exist stay zero in every stage's activation tile
-    for (int i = tid; i < NS * (C::X_BYTES / 16); i += C::THREADS) {
-        const int s = i / (C::X_BYTES / 16), c = i - s * (C::X_BYTES / 16);
-        *reinterpret_cast<uint4 *>(smem_raw + (size_t)s * p.stage_stride + x_off + c * 16) = make_uint4(0, 0, 0, 0);
-    }
+    // batch rows that do not exist read this row of zeros
+    for (int i = tid; i < p.x_row_bytes / 16; i += C::THREADS) reinterpret_cast<uint4 *>(zero_row)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
 
     if (warp == 0) {
         // ------------------------------ code producer (weights only: runs before the dependency wait) ----------
-        if (lane == 0) {
-            int r = r0, kt = kt0;
-            for (int i = 0; i < n_units; ++i) {
-                const int s = i % NS;
-                if (i >= NS && !mbar_wait(empty_bar(s), (uint32_t)((i / NS - 1) & 1), s_abort)) { *s_abort = 1; break; }
-                const int first_blk = (kt * 64) / p.bs, last_blk = (kt * 64 + 63) / p.bs;
-                const uint32_t sc_bytes = (uint32_t)(last_blk - first_blk + 1) * 256u;
-                const uint32_t dst = smem0 + (uint32_t)s * p.stage_stride;
-                mbar_arrive_expect_tx(full_bar(s), SK_TILE_BYTES + sc_bytes);
-                bulk_load(dst + w_off, p.tiles + ((size_t)r * p.k_tiles + kt) * SK_TILE_BYTES, SK_TILE_BYTES, full_bar(s));
-                bulk_load(dst + sc_off, p.scales_t + ((size_t)r * p.blocks_per_row + first_blk) * 128, sc_bytes, full_bar(s));
-                if (++kt == p.k_tiles) { kt = 0; ++r; }
+        // Lane s owns ring stage s.  A stage is one bulk copy of up to skt adjacent 8 KB tiles (they are contiguous in
+        // the tile-major layout) plus one of their scales: what limits a ring is the number of stage hand-overs per
+        // microsecond, not the bytes, so stages are made as large as the shared-memory budget allows.
+        if (lane < NS) {
+            StageWalk walk(u0, n_units, p.k_tiles, p.skt);
+            int sr, skt0, snk;
+            for (int i = 0; walk.next(sr, skt0, snk); ++i) {
+                if (i % NS != lane) continue;
+                if (i >= NS && !mbar_wait(empty_bar(lane), (uint32_t)((i / NS - 1) & 1), s_abort)) { *s_abort = 1; break; }
+                const int first_blk = (skt0 * 64) / p.bs, last_blk = ((skt0 + snk) * 64 - 1) / p.bs;
+                const uint32_t w_bytes = (uint32_t)snk * SK_TILE_BYTES, sc_bytes = (uint32_t)(last_blk - first_blk + 1) * 256u;
+                const uint32_t dst = smem0 + (uint32_t)lane * p.stage_stride;
+                mbar_arrive_expect_tx(full_bar(lane), w_bytes + sc_bytes);
+                bulk_load(dst, p.tiles + ((size_t)sr * p.k_tiles + skt0) * SK_TILE_BYTES, w_bytes, full_bar(lane));
+                bulk_load(dst + sc_off, p.scales_t + ((size_t)sr * p.blocks_per_row + first_blk) * 128, sc_bytes, full_bar(lane));
             }
         }
-    } else if (warp < C::FIRST_CONSUMER) {
-        // ------------------------------ activation producers ------------------------------
-        const int which = warp - 1;
+    } else if (warp == 1) {
+        // ------------------------------ activation producer ------------------------------
         const bool bf16 = p.dtype == ATLAS_DTYPE_BF16;
         asm volatile("griddepcontrol.wait;" ::: "memory");   // x comes from the earlier kernels of the stream
         const uint16_t *xg = reinterpret_cast<const uint16_t *>(p.x);
-        int kt = kt0;
         bool alive = true;
         const bool gathered_x = p.wait_flags != nullptr;
         if (gathered_x) {
@@ -264,47 +316,76 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
                 *s_abort = 1;
             }
         }
-        for (int i = 0; i < n_units; ++i) {
-            if (i % C::XP_WARPS == which) {
-                const int s = i % NS;
-                if (alive && i >= NS && !mbar_wait(empty_bar(s), (uint32_t)((i / NS - 1) & 1), s_abort)) {
+        // An activation stage holds, per batch row, the 64 * snk columns of a code stage as one run (rows
+        // x_row_bytes apart: 16 bytes of padding keep the consumers' paired reads of two rows on different banks).
+        // The ring is deeper than the codes' and is filled by one bulk copy per batch row, XS - 1 stages ahead, so
+        // that the latency of x is paid once after the dependency wait; bf16 is converted in place once landed.
+        StageWalk ahead(u0, n_units, p.k_tiles, p.skt), done(u0, n_units, p.k_tiles, p.skt);
+        int issued = 0;
+        // Requests the activations of up to `count` further stages.  Issuing a bulk copy occupies a thread for
+        // hundreds of cycles, so the (stage, batch row) copies are spread over the lanes.
+        auto issue = [&](int count) {
+            int sr[12], skt0[12], snk[12], n = 0;
+#pragma unroll
+            for (int c = 0; c < 12; ++c)
+                if (c < count && ahead.next(sr[n], skt0[n], snk[n])) ++n;
+            if (n == 0) return;
+            // stage `issued + c` must have been handed back by the consumers; then announce its bytes
+            for (int c = 0; c < n; ++c) {
+                const int st = issued + c, s = st % XS;
+                if (alive && st >= XS && !mbar_wait(xempty_bar(s), (uint32_t)((st / XS - 1) & 1), s_abort)) {
                     alive = false;
                     *s_abort = 1;
                 }
-                unsigned char *xs = smem_raw + (size_t)s * p.stage_stride + x_off;
-                // 16-byte chunk ch of row rr goes to position ch ^ (rr & 1): the consumers' paired reads of two rows
-                // then fall on different banks
-                for (int idx = lane; idx < p.m * 8; idx += 32) {
-                    const int rr = idx >> 3, ch = idx & 7;
-                    const uint16_t *src = xg + (size_t)rr * p.ldx + kt * 64 + ch * 8;
-                    uint4 v;
-                    if (p.x_vec_ok) {
-                        // data stored by peers during this kernel's life must not come through the non-coherent path
-                        v = gathered_x ? __ldcg(reinterpret_cast<const uint4 *>(src)) : __ldg(reinterpret_cast<const uint4 *>(src));
-                    } else if (gathered_x) {
-                        const volatile uint16_t *vs = src;
-                        v.x = vs[0] | (uint32_t)vs[1] << 16;
-                        v.y = vs[2] | (uint32_t)vs[3] << 16;
-                        v.z = vs[4] | (uint32_t)vs[5] << 16;
-                        v.w = vs[6] | (uint32_t)vs[7] << 16;
-                    } else {
-                        v.x = src[0] | (uint32_t)src[1] << 16;
-                        v.y = src[2] | (uint32_t)src[3] << 16;
-                        v.z = src[4] | (uint32_t)src[5] << 16;
-                        v.w = src[6] | (uint32_t)src[7] << 16;
-                    }
-                    if (bf16) {
-                        v.x = bf16x2_to_f16x2(v.x);
-                        v.y = bf16x2_to_f16x2(v.y);
-                        v.z = bf16x2_to_f16x2(v.z);
-                        v.w = bf16x2_to_f16x2(v.w);
-                    }
-                    *reinterpret_cast<uint4 *>(xs + rr * 128 + ((ch ^ (rr & 1)) << 4)) = v;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_bar(s));
             }
-            if (++kt == p.k_tiles) kt = 0;
+            if (p.x_vec_ok) {
+                if (lane < n) mbar_arrive_expect_tx(xraw_bar((issued + lane) % XS), (uint32_t)(p.m * snk[lane] * 128));
+                __syncwarp();
+                for (int pr = lane; pr < n * p.m; pr += 32) {
+                    const int c = pr / p.m, rr = pr - c * p.m, s = (issued + c) % XS;
+                    bulk_load(smem_u32(x_ring + (size_t)s * p.x_stride + rr * p.x_row_bytes),
+                              xg + (size_t)rr * p.ldx + skt0[c] * 64, (uint32_t)snk[c] * 128u, xraw_bar(s));
+                }
+            } else {
+                // rows of x that do not allow 16-byte accesses: plain 2-byte loads, published like a landed copy
+                for (int c = 0; c < n; ++c) {
+                    unsigned char *xs = x_ring + (size_t)((issued + c) % XS) * p.x_stride;
+                    for (int idx = lane; idx < p.m * snk[c] * 32; idx += 32) {
+                        const int rr = idx / (snk[c] * 32), c2 = idx - rr * (snk[c] * 32);
+                        const volatile uint16_t *src = xg + (size_t)rr * p.ldx + skt0[c] * 64 + c2 * 2;
+                        *reinterpret_cast<uint32_t *>(xs + rr * p.x_row_bytes + c2 * 4) = src[0] | (uint32_t)src[1] << 16;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(xraw_bar((issued + c) % XS));
+                }
+            }
+            issued += n;
+        };
+        issue(XS - 1);   // everything the ring holds but one stage, at once
+        int sr, skt0, snk;
+        for (int i = 0; done.next(sr, skt0, snk); ++i) {
+            const int s = i % XS;
+            if (alive && !mbar_wait(xraw_bar(s), (uint32_t)((i / XS) & 1), s_abort)) {
+                alive = false;
+                *s_abort = 1;
+            }
+            if (bf16) {
+                unsigned char *xs = x_ring + (size_t)s * p.x_stride;
+                const int per_row = snk * 8;   // 16-byte pieces per batch row
+                for (int idx = lane; idx < p.m * per_row; idx += 32) {
+                    const int rr = idx / per_row, pc = idx - rr * per_row;
+                    uint4 *at = reinterpret_cast<uint4 *>(xs + rr * p.x_row_bytes + pc * 16);
+                    uint4 v = *at;
+                    v.x = bf16x2_to_f16x2(v.x);
+                    v.y = bf16x2_to_f16x2(v.y);
+                    v.z = bf16x2_to_f16x2(v.z);
+                    v.w = bf16x2_to_f16x2(v.w);
+                    *at = v;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xfull_bar(s));
+            issue(1);
         }
     } else {
         // ------------------------------ consumers ------------------------------
@@ -315,77 +396,70 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
         const bool gathered_x = p.wait_flags != nullptr;
         const uint16_t *xg = reinterpret_cast<const uint16_t *>(p.x);
 
-        // outlier list of the first segment: weights only, requested before the dependency wait
+        // Outliers.  The strip's entries (row, column; sorted by column at repack time) of the columns a ring stage
+        // covers are one contiguous run, whose end comes from the chunk_ptr table: lane l keeps the boundary after
+        // stage cw_base + l of the segment (two windows of 32), and lane l of cur / nxt keeps entry win_base (+32) + l.
+        // Everything here is weight-side data, requested ahead; the activations come from the stage in shared memory.
         auto seg_end_kt = [&](int kt_begin, int left) { return min(p.k_tiles, kt_begin + left); };
-        int e_cur = 0, e_end = 0, win_base = 0;
-        uint32_t cur_ent = 0xff000000u, nxt_ent = 0xff000000u, cur_val = 0, nxt_val = 0;
-        auto load_window = [&](int base, uint32_t &ent, uint32_t &val) {
+        int e_cur = 0, e_end = 0, win_base = 0, cw_base = 0, seg_ka = 0, seg_kb = 0;
+        // three windows of 32 entries (the one in use and two requested ahead: ~16 stages of lead at the benchmark's
+        // outlier density), and the first window of the next segment, requested a few stages before it starts
+        uint32_t cur_ent = 0xff000000u, nxt_ent = 0xff000000u, nx2_ent = 0xff000000u, pre_ent = 0xff000000u;
+        uint32_t cur_val = 0, nxt_val = 0, nx2_val = 0, pre_val = 0;
+        int cwin = 0, cnext = 0, pre_cwin = 0;
+        bool have_pre = false;
+        const int32_t *seg_cp = nullptr;
+        auto load_window = [&](int base, int end, uint32_t &ent, uint32_t &val) {
             ent = 0xff000000u;
             val = 0;
-            if (base + lane < e_end) { ent = __ldg(p.entries + base + lane); val = __ldg(p.ovals + base + lane); }
+            if (base + lane < end) { ent = __ldg(p.entries + base + lane); val = __ldg(p.ovals + base + lane); }
         };
-        auto start_outliers = [&](int ea, int eb) {
+        auto bounds_of = [&](const int32_t *cp, int ka_, int kb_, int first_stage) {
+            // boundary after stage first_stage + lane of a segment [ka_, kb_): the entry index at its end column
+            return (int)__ldg(cp + min(ka_ + (first_stage + lane + 1) * p.skt, kb_));
+        };
+        auto load_bounds = [&](int first_stage) { return bounds_of(seg_cp, seg_ka, seg_kb, first_stage); };
+        auto start_segment = [&](int row_tile, int ka_, int kb_, int ea, int eb) {
+            seg_cp = p.chunk_ptr + ((size_t)row_tile * 8 + w) * (p.k_tiles + 1);
+            seg_ka = ka_;
+            seg_kb = kb_;
             e_cur = ea;
             e_end = eb;
             win_base = ea;
-            load_window(ea, cur_ent, cur_val);
-            load_window(ea + 32, nxt_ent, nxt_val);
+            cw_base = 0;
+            if (have_pre) {
+                cur_ent = pre_ent;
+                cur_val = pre_val;
+                cwin = pre_cwin;
+                have_pre = false;
+            } else {
+                load_window(ea, eb, cur_ent, cur_val);
+                cwin = load_bounds(0);
+            }
+            load_window(ea + 32, eb, nxt_ent, nxt_val);
+            load_window(ea + 64, eb, nx2_ent, nx2_val);
+            cnext = load_bounds(32);
         };
         {
             const int32_t *cp = p.chunk_ptr + ((size_t)r0 * 8 + w) * (p.k_tiles + 1);
-            start_outliers(__ldg(cp + kt0), __ldg(cp + seg_end_kt(kt0, n_units)));
+            const int kb0 = seg_end_kt(kt0, n_units);
+            start_segment(r0, kt0, kb0, __ldg(cp + kt0), __ldg(cp + kb0));
         }
         asm volatile("griddepcontrol.wait;" ::: "memory");   // x, y and the workspace belong to the stream from here on
 
         float acc[MT][4];
-        uint32_t og_rv[4];          // pending outlier group: row << 16 | fp16 value per K slot of this lane
-        uint32_t og_x[MT][4];       //   and the activations gathered for it (raw 16-bit patterns)
-        bool og_pending = false;
-        auto outlier_gather = [&]() {     // entries e_cur .. e_cur + 15: fetch their activations
-            const int off = e_cur - win_base;   // 0 or 16
+        // where this lane finds the activations of batch row nt * 8 + g inside a stage: its own row, or the zero row
+        int x_row_off[MT];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int slot = 2 * tig + (q & 1) + (q >> 1) * 8;
-                const uint32_t ent = __shfl_sync(0xffffffffu, cur_ent, off + slot);
-                const uint32_t val = __shfl_sync(0xffffffffu, cur_val, off + slot);
-                og_rv[q] = (ent >> 24) << 16 | val;     // row 255 (no entry) matches no lane
-                const uint32_t col = ent & 0xffffffu;   // 0 for missing entries: stays in range
-#pragma unroll
-                for (int nt = 0; nt < MT; ++nt) {
-                    const int mm = nt * 8 + g;
-                    const uint16_t *xp = xg + (size_t)(mm < p.m ? mm : 0) * p.ldx + col;
-                    og_x[nt][q] = gathered_x ? (uint32_t)__ldcg(xp) : (uint32_t)__ldg(xp);
-                }
-            }
-            og_pending = true;
-            e_cur += 16;
-            if (e_cur - win_base == 32) {
-                cur_ent = nxt_ent;
-                cur_val = nxt_val;
-                win_base += 32;
-                load_window(win_base + 32, nxt_ent, nxt_val);
-            }
-        };
-        auto outlier_mma = [&]() {
-            uint32_t rws[4], vals[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) { rws[q] = og_rv[q] >> 16; vals[q] = og_rv[q] & 0xffffu; }
-            const uint32_t ug = (uint32_t)g;
-            const uint32_t a0 = (rws[0] == ug ? vals[0] : 0u) | (rws[1] == ug ? vals[1] : 0u) << 16;
-            const uint32_t a1 = (rws[0] == ug + 8 ? vals[0] : 0u) | (rws[1] == ug + 8 ? vals[1] : 0u) << 16;
-            const uint32_t a2 = (rws[2] == ug ? vals[2] : 0u) | (rws[3] == ug ? vals[3] : 0u) << 16;
-            const uint32_t a3 = (rws[2] == ug + 8 ? vals[2] : 0u) | (rws[3] == ug + 8 ? vals[3] : 0u) << 16;
-#pragma unroll
-            for (int nt = 0; nt < MT; ++nt) {
-                uint32_t b0 = og_x[nt][0] | og_x[nt][1] << 16, b1 = og_x[nt][2] | og_x[nt][3] << 16;
-                if (bf16) { b0 = bf16x2_to_f16x2(b0); b1 = bf16x2_to_f16x2(b1); }
-                mma_f16(acc[nt], a0, a1, a2, a3, b0, b1);
-            }
-            og_pending = false;
-        };
+        for (int nt = 0; nt < MT; ++nt) x_row_off[nt] = nt * 8 + g < p.m ? (nt * 8 + g) * p.x_row_bytes : -1;
 
         bool alive = true;
-        int r = r0, kt = kt0, left = n_units, i = 0, seg = 0;
+        int r = r0, kt = kt0, left = n_units, seg = 0;
+        int s = 0, xsi = 0;                  // ring positions of the stage being consumed
+        uint32_t ph = 0, xph = 0;            // and the parities of their current rounds
+        bool first_stage = true;
+        const int bt = POST ? p.bs >> 6 : 1; // tiles per scale block
+        constexpr int NA = MT <= 2 ? 2 : 1;  // independent accumulator chains
         while (left > 0) {
             const int ka = kt, kb = seg_end_kt(kt, left);
             // the next segment's outlier range (its row tile starts at column 0): requested now, used when it starts
@@ -395,69 +469,185 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
                 nxt_ea = __ldg(cp);
                 nxt_eb = __ldg(cp + seg_end_kt(0, left - (kb - ka)));
             }
+            float part[NA][MT][4];   // dense sums: of the current block (POST) or of the segment
+#pragma unroll
+            for (int a = 0; a < NA; ++a)
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) part[a][nt][j] = 0.f;
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
-            // a segment that is not the first waits a few steps for its entry windows before touching them
-            int o_hold = seg == 0 ? 0 : 4;
+            int seg_stage = 0;                       // stage index inside the segment
+            int blk_left = POST ? bt - kt % bt : 0;  // tiles until the current scale block ends
 
-            for (; kt < kb; ++kt, ++i) {
-                const int s = i % NS;
-                bool got = !alive || mbar_wait(full_bar(s), (uint32_t)((i / NS) & 1), s_abort);
+            while (kt < kb) {
+                const int snk = min(p.skt, kb - kt);       // tiles in this stage (the same cut the producers make)
+                bool got = !alive || mbar_wait(xfull_bar(xsi), xph, s_abort);
                 // the first stage also stands for the activation producer's wait for the other ranks
-                for (int extra = 0; !got && gathered_x && i == 0 && extra < 64 && !*s_abort; ++extra)
-                    got = mbar_wait(full_bar(s), 0u, s_abort);
+                for (int extra = 0; !got && gathered_x && first_stage && extra < 64 && !*s_abort; ++extra)
+                    got = mbar_wait(xfull_bar(xsi), 0u, s_abort);
+                got = got && (!alive || mbar_wait(full_bar(s), ph, s_abort));
+                first_stage = false;
                 if (!got) {
                     alive = false;
                     *s_abort = 1;
                 }
                 const unsigned char *stg = smem_raw + (size_t)s * p.stage_stride;
-                const uint4 wa = *reinterpret_cast<const uint4 *>(stg + w_off + w * 1024 + lane * 16);          // row g of the strip
-                const uint4 wb = *reinterpret_cast<const uint4 *>(stg + w_off + w * 1024 + 512 + lane * 16);    // row g + 8
-                const int col = kt * 64 + tig * 16;
-                const int kbl = (p.bs_shift >= 0 ? (col >> p.bs_shift) - ((kt * 64) >> p.bs_shift)
-                                                 : col / p.bs - (kt * 64) / p.bs);
-                const uint16_t *scs = reinterpret_cast<const uint16_t *>(stg + sc_off) + kbl * 128 + w * 16 + g;
-                const __half2 sa2 = __half2half2(__ushort_as_half(scs[0]));
-                const __half2 sb2 = __half2half2(__ushort_as_half(scs[8]));
-                const uint32_t wav[4] = {wa.x, wa.y, wa.z, wa.w};
-                const uint32_t wbv[4] = {wb.x, wb.y, wb.z, wb.w};
-                uint32_t a_lo[4], a_hi[4], b_lo[4], b_hi[4];
+                const unsigned char *xst = x_ring + (size_t)xsi * p.x_stride;
+                const int first_blk = p.bs_shift >= 0 ? (kt * 64) >> p.bs_shift : (kt * 64) / p.bs;
+                // ---- this warp's codes and scales of the whole stage go to registers and the stage goes back to the
+                // producer at once: a code stage that is held while it is multiplied is a stage that is not in flight
+                uint4 wreg[SK_SKT][2];
+                uint32_t screg[SK_SKT];   // scale of row g | scale of row g + 8 << 16, per tile (of the lane's 16 columns)
+                {
+                    const unsigned char *wp = stg + w * 1024 + lane * 16;
+                    const uint16_t *sc_lane = reinterpret_cast<const uint16_t *>(stg + sc_off) + w * 16 + g;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    dequant4(wav[q], sa2, a_lo[q], a_hi[q]);
-                    dequant4(wbv[q], sb2, b_lo[q], b_hi[q]);
-                }
-#pragma unroll
-                for (int nt = 0; nt < MT; ++nt) {
-                    const unsigned char *xr = stg + x_off + (nt * 8 + g) * 128;
-                    const uint4 x0 = *reinterpret_cast<const uint4 *>(xr + (((2 * tig) ^ (g & 1)) << 4));
-                    const uint4 x1 = *reinterpret_cast<const uint4 *>(xr + (((2 * tig + 1) ^ (g & 1)) << 4));
-                    if (nt == MT - 1) {
-                        // everything this warp needs from the stage is in registers: hand it back
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(empty_bar(s));
+                    for (int j = 0; j < SK_SKT; ++j) {
+                        if (j < snk) {
+                            wreg[j][0] = *reinterpret_cast<const uint4 *>(wp + j * SK_TILE_BYTES);          // row g of the strip
+                            wreg[j][1] = *reinterpret_cast<const uint4 *>(wp + j * SK_TILE_BYTES + 512);    // row g + 8
+                            const int col = (kt + j) * 64 + (POST ? 0 : tig * 16);
+                            const int kbl = (p.bs_shift >= 0 ? col >> p.bs_shift : col / p.bs) - first_blk;
+                            screg[j] = (uint32_t)sc_lane[kbl * 128] | (uint32_t)sc_lane[kbl * 128 + 8] << 16;
+                        }
                     }
-                    const uint32_t xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_bar(s));
+                }
+                if (!have_pre && left > kb - ka && (seg_stage == 3 || kt + snk >= kb)) {
+                    // the next segment's first entries and stage boundaries, a few stages before they are needed
+                    const int32_t *ncp = p.chunk_ptr + ((size_t)(r + 1) * 8 + w) * (p.k_tiles + 1);
+                    load_window(nxt_ea, nxt_eb, pre_ent, pre_val);
+                    pre_cwin = bounds_of(ncp, 0, seg_end_kt(0, left - (kb - ka)), 0);
+                    have_pre = true;
+                }
+                {
+                    // ---- outliers of the stage's columns, 16 per MMA, activations from the stage itself ----------
+                    int o = seg_stage - cw_base;
+                    if (o >= 32) {
+                        cwin = cnext;
+                        cw_base += 32;
+                        cnext = load_bounds(cw_base + 32);
+                        o -= 32;
+                    }
+                    const int e_hi = __shfl_sync(0xffffffffu, cwin, o);
+                    const int col_base = kt * 64;
+                    while (e_cur < e_hi) {
+                        if (e_cur - win_base >= 32) {
+                            cur_ent = nxt_ent;
+                            cur_val = nxt_val;
+                            nxt_ent = nx2_ent;
+                            nxt_val = nx2_val;
+                            win_base += 32;
+                            load_window(win_base + 64, e_end, nx2_ent, nx2_val);
+                        }
+                        const int off = e_cur - win_base;   // 0..31; the group may reach into the next window
+                        uint32_t rv[4];
+                        int xo[4];                           // byte offset of the entry's column inside a batch row of the stage
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        mma_f16(acc[nt], a_lo[q], b_lo[q], a_hi[q], b_hi[q], xv[2 * q], xv[2 * q + 1]);
+                        for (int q = 0; q < 4; ++q) {
+                            const int slot = 2 * tig + (q & 1) + (q >> 1) * 8;
+                            const int at = off + slot;
+                            uint32_t ent = __shfl_sync(0xffffffffu, cur_ent, at & 31);
+                            uint32_t val = __shfl_sync(0xffffffffu, cur_val, at & 31);
+                            if (off > 16) {                  // warp-uniform: only then can a slot fall into the next window
+                                const uint32_t ent2 = __shfl_sync(0xffffffffu, nxt_ent, at & 31);
+                                const uint32_t val2 = __shfl_sync(0xffffffffu, nxt_val, at & 31);
+                                if (at >= 32) { ent = ent2; val = val2; }
+                            }
+                            const bool valid = e_cur + slot < e_hi;
+                            rv[q] = valid ? (ent >> 24) << 16 | val : 0x00ff0000u;   // row 255 matches no lane
+                            xo[q] = valid ? ((int)(ent & 0xffffffu) - col_base) * 2 : 0;    // 0 .. snk * 128 - 2
+                        }
+                        uint32_t rws[4], vals[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) { rws[q] = rv[q] >> 16; vals[q] = rv[q] & 0xffffu; }
+                        const uint32_t ug = (uint32_t)g;
+                        const uint32_t a0 = (rws[0] == ug ? vals[0] : 0u) | (rws[1] == ug ? vals[1] : 0u) << 16;
+                        const uint32_t a1 = (rws[0] == ug + 8 ? vals[0] : 0u) | (rws[1] == ug + 8 ? vals[1] : 0u) << 16;
+                        const uint32_t a2 = (rws[2] == ug ? vals[2] : 0u) | (rws[3] == ug ? vals[3] : 0u) << 16;
+                        const uint32_t a3 = (rws[2] == ug + 8 ? vals[2] : 0u) | (rws[3] == ug + 8 ? vals[3] : 0u) << 16;
+#pragma unroll
+                        for (int nt = 0; nt < MT; ++nt) {
+                            uint32_t xq[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                xq[q] = x_row_off[nt] >= 0 ? *reinterpret_cast<const uint16_t *>(xst + x_row_off[nt] + xo[q]) : 0u;
+                            mma_f16(acc[nt], a0, a1, a2, a3, xq[0] | xq[1] << 16, xq[2] | xq[3] << 16);
+                        }
+                        e_cur = min(e_cur + 16, e_hi);
+                    }
                 }
-                // outliers ride along: on odd steps the next 16 entries' activations are requested, on even steps the
-                // group requested a step ago becomes one more MMA (an entry window of 32 then lasts four steps, about
-                // the latency of the load that refills it)
-                if (o_hold > 0) {
-                    --o_hold;
-                } else if (i & 1) {
-                    if (!og_pending && e_cur < e_end) outlier_gather();
-                } else if (og_pending) {
-                    outlier_mma();
+                // ---- dense part, from registers; the activations come tile by tile from their own ring -------------
+#pragma unroll
+                for (int j = 0; j < SK_SKT; ++j) {
+                    if (j < snk) {
+                        const uint32_t wav[4] = {wreg[j][0].x, wreg[j][0].y, wreg[j][0].z, wreg[j][0].w};
+                        const uint32_t wbv[4] = {wreg[j][1].x, wreg[j][1].y, wreg[j][1].z, wreg[j][1].w};
+                        uint32_t a_lo[4], a_hi[4], b_lo[4], b_hi[4];
+                        if (POST) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                codes4(wav[q], a_lo[q], a_hi[q]);
+                                codes4(wbv[q], b_lo[q], b_hi[q]);
+                            }
+                        } else {
+                            const __half2 sa2 = __half2half2(__ushort_as_half((unsigned short)(screg[j] & 0xffffu)));
+                            const __half2 sb2 = __half2half2(__ushort_as_half((unsigned short)(screg[j] >> 16)));
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                dequant4(wav[q], sa2, a_lo[q], a_hi[q]);
+                                dequant4(wbv[q], sb2, b_lo[q], b_hi[q]);
+                            }
+                        }
+                        const bool fold = POST && (--blk_left == 0 || kt == kb - 1);   // this tile ends its scale block
+                        const float sca_f = __half2float(__ushort_as_half((unsigned short)(screg[j] & 0xffffu)));
+                        const float scb_f = __half2float(__ushort_as_half((unsigned short)(screg[j] >> 16)));
+                        if (fold) blk_left = bt;
+#pragma unroll
+                        for (int nt = 0; nt < MT; ++nt) {
+                            const unsigned char *xr = x_row_off[nt] >= 0 ? xst + x_row_off[nt] + j * 128 : zero_row;
+                            const uint4 x0 = *reinterpret_cast<const uint4 *>(xr + tig * 32);
+                            const uint4 x1 = *reinterpret_cast<const uint4 *>(xr + tig * 32 + 16);
+                            if (nt == MT - 1 && j == snk - 1) {
+                                // the last activations of the stage are in registers: hand the activation stage back
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(xempty_bar(xsi));
+                            }
+                            const uint32_t xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                mma_f16(part[q % NA][nt], a_lo[q], b_lo[q], a_hi[q], b_hi[q], xv[2 * q], xv[2 * q + 1]);
+                            if (fold) {
+#pragma unroll
+                                for (int a = 0; a < NA; ++a) {
+                                    acc[nt][0] = fmaf(sca_f, part[a][nt][0], acc[nt][0]);
+                                    acc[nt][1] = fmaf(sca_f, part[a][nt][1], acc[nt][1]);
+                                    acc[nt][2] = fmaf(scb_f, part[a][nt][2], acc[nt][2]);
+                                    acc[nt][3] = fmaf(scb_f, part[a][nt][3], acc[nt][3]);
+#pragma unroll
+                                    for (int c = 0; c < 4; ++c) part[a][nt][c] = 0.f;
+                                }
+                            }
+                        }
+                        ++kt;
+                    }
                 }
+                if (++s == NS) { s = 0; ph ^= 1u; }
+                if (++xsi == XS) { xsi = 0; xph ^= 1u; }
+                ++seg_stage;
             }
-            while (og_pending || e_cur < e_end) {   // what the dense steps did not cover
-                if (og_pending) outlier_mma();
-                if (e_cur < e_end) outlier_gather();
+            if (!POST) {   // the dense sums were already in the weight's own units
+#pragma unroll
+                for (int a = 0; a < NA; ++a)
+#pragma unroll
+                    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[nt][c] += part[a][nt][c];
             }
 
             // ---- the strip's sums go to the CTA's staging tile [row][batch column] ----------------------
@@ -504,9 +694,9 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
                     const int mm = idx >> 7, row = idx & 127;
                     __stcg(mine + idx, s_out[row * C::OUT_LD + mm]);
                 }
-                __threadfence();
                 consumer_bar();
                 if (ct == 0) {
+                    __threadfence();   // the other consumers' stores are ordered before this by the barrier
                     const unsigned int t = atomicAdd(p.tickets + r, 1u);
                     __threadfence();
                     *s_ticket = (int)t;
@@ -532,7 +722,7 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
             kt = 0;
             ++r;
             ++seg;
-            if (left > 0) start_outliers(nxt_ea, nxt_eb);
+            if (left > 0) start_segment(r, 0, seg_end_kt(0, left), nxt_ea, nxt_eb);
         }
     }
 
@@ -568,9 +758,9 @@ int stream_sm_count() {
     return sms;
 }
 
-template <int MT>
+template <int MT, bool POST>
 int launch_stream(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = qlinear_stream_kernel<MT>;
+    auto kern = qlinear_stream_kernel<MT, POST>;
     static thread_local size_t configured = 0;
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -661,9 +851,6 @@ int stream_entry(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t
     p.blocks_per_row = (int)(n_cols / block_size);
     p.tile_rows = (int)ceil_div_i64(n_rows, 128);
     p.units = (long long)p.tile_rows * p.k_tiles;
-    // scale blocks a 64-column tile can touch: one when blocks are whole tiles, 64 / bs when they divide a tile
-    const int max_blk = block_size % 64 == 0 ? 1 : (64 % block_size == 0 ? 64 / block_size : 64 / block_size + 2);
-    p.scale_cap = max_blk * 256;
     p.x_vec_ok = (((uintptr_t)x & 15) == 0) && (ldx % 8 == 0);
     p.tickets = (unsigned int *)workspace;
     p.partials = (float *)((char *)workspace + SK_TICKET_BYTES);
@@ -696,16 +883,34 @@ int stream_entry(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t
         p.m = mg;
         p.x = (const char *)x + (size_t)m0 * ldx * 2;
         p.y = (char *)y + (size_t)m0 * ldy * 2;
-        const int x_bytes = mt * 8 * 128, out_bytes = 128 * mt * 8 * 4;
-        p.stage_stride = (SK_TILE_BYTES + p.scale_cap + x_bytes + 127) & ~127;
-        int ns = (SK_SMEM_BUDGET - out_bytes - 64) / (p.stage_stride + 16);
-        if (ns > 16) ns = 16;
-        ATLAS_RETURN_IF(ns < 2, ATLAS_ERR_UNSUPPORTED, "atlas_qlinear_stream: stage of %d bytes does not fit", p.stage_stride);
+        // Ring geometry.  A code stage is SK_SKT tiles of 64 columns (8 KB each) plus their scales; a consumer warp
+        // takes its share of a stage to registers and hands the stage back at once, so nearly the whole ring is in
+        // flight.  The activations of a stage (m rows) live in a ring of their own, which can be deeper (they
+        // can only be requested after the dependency wait, so their latency must be paid once, not per stage).
+        const int out_bytes = 128 * mt * 8 * 4;
+        const int skt = SK_SKT;
+        const int max_blk = block_size % 64 == 0 ? (skt * 64 + block_size - 1) / block_size + 1 : (skt * 64) / block_size + 2;
+        p.scale_cap = max_blk * 256;
+        p.x_row_bytes = skt * 128 + 16;
+        p.x_stride = mg * p.x_row_bytes;
+        p.stage_stride = (skt * SK_TILE_BYTES + p.scale_cap + 127) & ~127;
+        int ns = 6, xs = 0;
+        for (; ns >= 2; --ns) {
+            const int fixed = ns * (p.stage_stride + 16) + p.x_row_bytes + out_bytes + 64;
+            xs = (SK_SMEM_BUDGET - fixed) / (p.x_stride + 24);
+            if (xs >= 3) break;
+        }
+        if (xs > 12) xs = 12;
+        ATLAS_RETURN_IF(ns < 2 || xs < 2, ATLAS_ERR_UNSUPPORTED, "atlas_qlinear_stream: the rings do not fit in shared memory");
+        p.skt = skt;
         p.n_stages = ns;
-        const size_t smem = (size_t)ns * p.stage_stride + out_bytes + 16 * ns + 64;
-        if (mt == 1) rc = launch_stream<1>(p, grid, smem, st);
-        else if (mt == 2) rc = launch_stream<2>(p, grid, smem, st);
-        else rc = launch_stream<4>(p, grid, smem, st);
+        p.x_stages = xs;
+        const size_t smem = (size_t)ns * p.stage_stride + (size_t)xs * p.x_stride + p.x_row_bytes + out_bytes +
+                            16 * ns + 24 * xs + 64;
+        const bool post = block_size % 64 == 0 && p.bs_shift >= 0;   // blocks of whole tiles: integer codes into the MMA
+        if (mt == 1) rc = post ? launch_stream<1, true>(p, grid, smem, st) : launch_stream<1, false>(p, grid, smem, st);
+        else if (mt == 2) rc = post ? launch_stream<2, true>(p, grid, smem, st) : launch_stream<2, false>(p, grid, smem, st);
+        else rc = launch_stream<4, false>(p, grid, smem, st);
         if (rc) return rc;
     }
     return ATLAS_OK;
@@ -739,3 +944,5 @@ extern "C" int atlas_qlinear_stream_gather(const void *x, int dtype, int64_t m, 
                                outlier_vals_sorted, n_rows, n_cols, block_size, bias, nullptr, ldy, workspace,
                                workspace_bytes, status, stream, gather);
 }
+
+

@@ -21,7 +21,10 @@ import torch.nn as nn
 from .. import _capi
 from ..quant.adaptive_quantizer import QuantizedTensor
 
-# rows of x up to which the streaming kernel is used (one pass over the weight); above it the tcgen05 kernel
+# rows of x up to which the per-strip streaming kernel is used (8 rows per pass over the weight); above it the
+# tcgen05 kernel.  The persistent streaming kernel takes up to STREAM_MAX_ROWS rows in one pass; it is what the
+# column-parallel linear with the fused gather runs on and can be asked for with force="stream".
+GEMV_MAX_ROWS = 16
 STREAM_MAX_ROWS = 32
 
 _VERBOSE = os.environ.get("ATLAS_VERBOSE", "0") not in ("", "0")
@@ -127,8 +130,8 @@ def quantized_linear_forward(x: torch.Tensor, layout: KernelLayout, bias: Option
                              force: Optional[str] = None) -> torch.Tensor:
     """``x @ W^T + bias`` on CUDA tensors through the C ABI.
 
-    ``force``: "stream" (persistent streaming kernel), "gemm" (tcgen05 kernel) or "gemv" (the per-strip
-    streaming kernel); default: "stream" up to 32 rows of x, "gemm" above."""
+    ``force``: "gemv" (per-strip streaming kernel), "gemm" (tcgen05 kernel) or "stream" (persistent streaming
+    kernel, one pass for up to 32 rows); default: "gemv" up to 16 rows of x, "gemm" above."""
     L = _capi.load()
     dev = x.device
     if x.dtype == torch.float16:
@@ -153,7 +156,7 @@ def quantized_linear_forward(x: torch.Tensor, layout: KernelLayout, bias: Option
         b = bias if bias.dtype == torch.float16 else bias.to(torch.float16)
         b = b.contiguous()
     if force is None:
-        force = "stream" if m <= STREAM_MAX_ROWS else "gemm"
+        force = "gemv" if m <= GEMV_MAX_ROWS else "gemm"
     if force not in ("stream", "gemv", "gemm"):
         raise ValueError(f"force={force!r}")
     args = [x2.data_ptr(), dtype, m, ldx, layout.tiles.data_ptr(), layout.scales_tiled.data_ptr(),
@@ -220,9 +223,9 @@ class FusedLinearGroup:
     The reference issues q/k/v (and gate/up) as separate ``F.linear`` calls on the same input
     (integration/atlas_wrappers.py:67, once per module).  Here the members' kernel layouts are joined row-wise
     (``concat_layouts``); the first member that is called with an input computes the joined product and the
-    other members, called with the very same tensor, return their slice of it.  A member called with any
-    other input, or with more rows than the streaming kernel takes in one pass, computes just its own rows
-    from its view of the joined layout.  A member's slice equals its stand-alone output up to the rounding of
+    other members, called with the very same tensor, return their slice of it (for prompt-sized inputs this
+    also means one bf16 -> fp16 conversion of the activations instead of one per member).  A member called
+    with any other input computes the joined product anew.  A member's slice equals its stand-alone output up to the rounding of
     the fp32 partial sums (the K range of a row tile is cut between CTAs at other places when the launch
     covers more rows), not bit for bit.
     """
@@ -270,7 +273,7 @@ class FusedLinearGroup:
         if x.device.type != "cuda" or x.dtype not in (torch.float16, torch.bfloat16):
             return None
         rows = x.numel() // x.shape[-1] if x.shape[-1] else 0
-        if rows == 0 or rows > STREAM_MAX_ROWS:
+        if rows == 0:
             return None
         if self.layout is None or self.layout.tiles.device != x.device:
             self.build(x.device)
