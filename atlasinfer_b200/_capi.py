@@ -23,7 +23,7 @@ EXPORTS = (
     "atlas_quantize_workspace_bytes", "atlas_quantize", "atlas_quantize_noalloc", "atlas_dequantize",
     "atlas_tiles_bytes", "atlas_repack", "atlas_qlinear_gemv",
     "atlas_qlinear_stream_workspace_bytes", "atlas_qlinear_stream", "atlas_qlinear_stream_gather",
-    "atlas_peer_wait", "atlas_peer_alloc", "atlas_peer_free", "atlas_peer_export", "atlas_peer_import",
+    "atlas_peer_wait", "atlas_peer_push", "atlas_peer_alloc", "atlas_peer_free", "atlas_peer_export", "atlas_peer_import",
     "atlas_peer_release",
     "atlas_qlinear_gemm_workspace_bytes", "atlas_qlinear_gemm",
 )
@@ -89,6 +89,8 @@ def load() -> ctypes.CDLL:
     L.atlas_qlinear_stream_gather.argtypes = lin[:13] + [i64, vp, sz, vp, vp, ctypes.POINTER(PeerGather)]
     L.atlas_peer_wait.restype = i32
     L.atlas_peer_wait.argtypes = [vp, i32, vp, i64, vp, vp]
+    L.atlas_peer_push.restype = i32
+    L.atlas_peer_push.argtypes = [vp, i64, i64, i64, i64, ctypes.POINTER(PeerGather), vp]
     L.atlas_peer_alloc.restype = i32
     L.atlas_peer_alloc.argtypes = [sz, ctypes.POINTER(vp)]
     L.atlas_peer_free.restype = i32

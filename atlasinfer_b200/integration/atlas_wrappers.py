@@ -69,17 +69,16 @@ _stream_workspaces = {}
 
 
 def stream_workspace(dev: torch.device) -> torch.Tensor:
-    """Scratch of the streaming kernel for the current stream of ``dev``: tickets and fp32 partial tiles.
+    """Scratch of the persistent streaming kernel on ``dev``: tickets and fp32 partial tiles.
 
-    Zero-filled once; every launch leaves it zero-filled where it must be.  One per (device, stream), because
-    launches that may overlap on the GPU must not share it."""
+    Zero-filled once; every launch leaves it zero-filled where it must be.  One per device: launches that use it
+    must be ordered with respect to each other."""
     index = dev.index if dev.index is not None else torch.cuda.current_device()
-    key = (index, int(torch.cuda.current_stream(dev).cuda_stream))
-    t = _stream_workspaces.get(key)
+    t = _stream_workspaces.get(index)
     if t is None:
         L = _capi.load()
         t = torch.zeros(int(L.atlas_qlinear_stream_workspace_bytes(STREAM_MAX_ROWS)), dtype=torch.uint8, device=dev)
-        _stream_workspaces[key] = t
+        _stream_workspaces[index] = t
     return t
 
 

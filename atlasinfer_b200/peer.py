@@ -2,10 +2,13 @@
 
 The reference is single-process; this is the multi-GPU form of its linear for the 70B-shaped configuration:
 rank r owns a slice of the output rows of every weight (``sharding.shard_rows``), and instead of writing its
-[m, N/g] shard locally and calling an NCCL all-gather (``sharding.gather_columns``), the streaming kernel stores
-the shard straight into every rank's gathered [m, N] buffer over NVLink and then publishes an arrival count; the
-next kernel that consumes the buffer waits (bounded) until all ranks have arrived.  The shards are 64 KB - 1.8 MB,
-so what this removes is the collective's launch and synchronisation latency, per linear.
+[m, N/g] shard locally and calling an NCCL all-gather (``sharding.gather_columns``), the rank stores the shard
+straight into every rank's gathered [m, N] buffer over NVLink and then publishes an arrival count; the next
+kernel that consumes the buffer waits (bounded) until all ranks have arrived.  The shards are 64 KB - 1.8 MB,
+so what this removes is the collective's launch and synchronisation latency, per linear.  The stores are either
+the epilogue of the streaming linear kernel (``kernel="stream"``: one launch does the linear, the wait and the
+gather) or a small push kernel behind the default linear kernels (``kernel="push"``: the per-strip kernel up to
+16 rows of x, the tcgen05 kernel above), with the wait as a kernel of its own in front.
 
 One process per GPU of one node.  ``PeerArena`` owns the memory the ranks share: each rank allocates an arena
 of the same size (``atlas_peer_alloc``: plain cudaMalloc memory), the ranks exchange CUDA IPC handles through
@@ -122,7 +125,10 @@ class GatheredLinear:
     completed as many gather launches as this rank (x is the output of the previous gathered launch)."""
 
     def __init__(self, arena: PeerArena, layout: aw.KernelLayout, m_max: int, dtype: torch.dtype,
-                 bias: Optional[torch.Tensor] = None, poll_limit: int = DEFAULT_POLL_LIMIT):
+                 bias: Optional[torch.Tensor] = None, poll_limit: int = DEFAULT_POLL_LIMIT, kernel: str = "stream"):
+        if kernel not in ("stream", "push"):
+            raise ValueError(f"kernel={kernel!r}")
+        self.kernel = kernel
         self.arena = arena
         self.layout = layout
         self.bias = bias
@@ -151,6 +157,17 @@ class GatheredLinear:
         if x2.stride(-1) != 1:
             x2 = x2.contiguous()
         m = x2.shape[0]
+        if self.kernel == "push":
+            if m > self.m_max:
+                raise ValueError(f"{m} rows of x; this gathered linear was set up for {self.m_max}")
+            if wait:
+                self.wait_for_all()
+            y = aw.quantized_linear_forward(x2, lay, self.bias)       # [m, n_local], this rank's columns
+            with torch.cuda.device(dev):
+                st = L.atlas_peer_push(y.data_ptr(), m, lay.n_rows * 2, y.stride(0) * 2, self.width * 2,
+                                       ctypes.byref(self._desc), _capi.stream_ptr(dev))
+            _capi.check(st, "atlas_peer_push")
+            return self.out[:m]
         if m > self.m_max or m > aw.STREAM_MAX_ROWS:
             raise ValueError(f"{m} rows of x; this gathered linear was set up for {min(self.m_max, aw.STREAM_MAX_ROWS)}")
         dtype = _capi.DTYPE_F16 if x.dtype == torch.float16 else _capi.DTYPE_BF16

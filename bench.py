@@ -392,7 +392,8 @@ def measure_tp70b(rank, world, steps, warmup, barrier):
     Every rank owns rows [r*N/g, (r+1)*N/g) of each linear (8 distinct layers, cycled ten times to stand for the
     80 layers; one layer's shards already exceed L2), q/k/v and gate/up fused into one launch each, and the
     [32, N/g] output shards are all-gathered after every launch: by NCCL (`nccl_allgather`), or by the ranks'
-    own peer stores into symmetric buffers followed by a flag exchange (`peer_stores`, see
+    own peer stores into symmetric buffers followed by a flag exchange (`peer_stores_fused`: in the streaming
+    linear kernel's epilogue; `peer_push`: a push kernel behind the default linear kernels; see
     atlasinfer_b200/peer.py).  Returns ms per token for each, the weight-streaming-only time and the aggregate
     algorithmic GB/s."""
     import torch.distributed as dist
@@ -432,11 +433,13 @@ def measure_tp70b(rank, world, steps, warmup, barrier):
             run, mode = fn, "eager"
         secs = allmax(time_steps(run, steps, warmup, barrier), world, dev)
         out[name] = dict(ms_per_token=secs / steps * 1e3, launch=mode)
-    if world > 1:
+    # the ranks' own peer stores instead of the collective: fused into the streaming linear kernel, or as a push
+    # kernel behind the default linear kernels (at one rank: the same launches, stores to the own buffer only)
+    for name, kernel in (("peer_stores_fused", "stream"), ("peer_push", "push")):
         try:
-            out["peer_stores"] = measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, world, dev)
-        except Exception as e:  # noqa: BLE001 - keep the NCCL figures
-            out["peer_stores"] = dict(error=repr(e))
+            out[name] = measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, rank, world, dev, kernel)
+        except Exception as e:  # noqa: BLE001 - keep the other figures
+            out[name] = dict(error=repr(e))
     nbytes = sum(l.nbytes(m) for l in model) * reps
     tot = torch.tensor([float(nbytes)], dtype=torch.float64, device=dev)
     if world > 1:
@@ -456,15 +459,16 @@ def measure_tp70b(rank, world, steps, warmup, barrier):
     return out
 
 
-def measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, world, dev):
-    """The column-parallel decode pass with the kernels' own peer stores instead of NCCL: one gathered buffer per
+def measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, rank, world, dev, kernel):
+    """The column-parallel decode pass with the ranks' own peer stores instead of NCCL: one gathered buffer per
     launch kind of a layer, every launch waiting (bounded) for the previous launch's arrivals from all ranks."""
     from atlasinfer_b200 import peer
     from atlasinfer_b200.integration import atlas_wrappers as aw
     per_layer = 4
-    arena = peer.PeerArena(sum(m * lay.n_rows * world * 2 + 256 for lay, _ in launches[:per_layer]) + 4096, dev)
+    arena = peer.PeerArena(sum(m * lay.n_rows * world * 2 + 256 for lay, _ in launches[:per_layer]) + 4096, dev,
+                           world=world, rank=rank, exchange=world > 1)
     try:
-        kinds = [peer.GatheredLinear(arena, lay, m, torch.bfloat16) for lay, _ in launches[:per_layer]]
+        kinds = [peer.GatheredLinear(arena, lay, m, torch.bfloat16, kernel=kernel) for lay, _ in launches[:per_layer]]
 
         def one_pass():
             for _ in range(reps):

@@ -165,13 +165,14 @@ ATLAS_API int atlas_repack(const int8_t *codes, int64_t n_codes, const void *out
  * never clears it.
  *
  * atlas_qlinear_gemv: decode shapes, any m >= 1 (intended for m <= 16).  HBM-
- * bound: up to 16 rows are served 8 at a time by a kernel that gives each CTA
+ * bound: the rows of x are served 8 at a time by a kernel that gives each CTA
  * one 16-row strip of the weight, streams its codes with 16-byte loads,
  * dequantises in registers and adds the outlier products in the same launch
- * (more rows, or activations that are not 16-byte aligned, go in groups of up
- * to 32 through a slower kernel with per-warp shared-memory rings).  Launched
- * with programmatic dependent launch: only weights are read before the
- * stream's earlier work has completed.
+ * (the passes after the first find most of the weight in L2).  Activations
+ * that are not 16-byte aligned are read two bytes at a time.  Launched with
+ * programmatic dependent launch: only weights are read before the stream's
+ * earlier work has completed.  The kernel has no bounded wait: `status` is
+ * accepted for symmetry and never written.
  *
  * atlas_qlinear_gemm: larger batches (any m >= 1 accepted).  The code tiles
  * come in by TMA, are dequantised by 16 warps straight into tensor memory as
@@ -271,6 +272,17 @@ ATLAS_API int atlas_qlinear_stream_gather(const void *x, int dtype, int64_t m, i
  * atlas kernels. */
 ATLAS_API int atlas_peer_wait(const uint32_t *flags, int world, const uint32_t *state, int64_t poll_limit,
                               int32_t *status, void *stream);
+
+/* The gather without the linear: copies this rank's finished shard `src`
+ * (`rows` x `row_bytes`, rows `src_pitch_bytes` apart) to gather->y_dst[d]
+ * (rows `dst_pitch_bytes` apart) on every rank d with plain peer stores and
+ * publishes the arrival exactly as atlas_qlinear_stream_gather does (same
+ * flags, same state, interchangeable launch by launch).  For shards computed
+ * by atlas_qlinear_gemv / atlas_qlinear_gemm: one small kernel instead of a
+ * collective.  gather->wait_flags and poll_limit are not used (the kernel
+ * waits for nothing; a consumer waits through atlas_peer_wait). */
+ATLAS_API int atlas_peer_push(const void *src, int64_t rows, int64_t row_bytes, int64_t src_pitch_bytes,
+                              int64_t dst_pitch_bytes, const AtlasPeerGather *gather, void *stream);
 
 /* Device memory that other processes of the node can map: plain cudaMalloc
  * memory (zero-filled), exported / imported as CUDA IPC handles (64 bytes).

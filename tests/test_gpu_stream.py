@@ -70,6 +70,7 @@ def test_dense_outliers_reach_every_outlier_branch(thr, cuda_device):
     gen = torch.Generator().manual_seed(5)
     wd = O.dequantize(o)
     for m, dtype, force in ((1, torch.float16, "stream"), (32, torch.bfloat16, "stream"), (5, torch.float16, "gemv"),
+                            (12, torch.bfloat16, "gemv"),
                             (200, torch.float16, "gemm"), (40, torch.bfloat16, "gemm")):
         x = torch.randn(m, 1024, generator=gen).to(dtype)
         y = _run(o, x, None, cuda_device, force)
@@ -246,10 +247,12 @@ def _arena_u32(arena, offset, count):
     return arena.local_tensor(offset, (count,), torch.int32)
 
 
-def test_peer_store_gather_with_emulated_ranks(cuda_device):
+@pytest.mark.parametrize("kernel", ["stream", "push"])
+def test_peer_store_gather_with_emulated_ranks(kernel, cuda_device):
     # four "ranks" in this process on one GPU, run one after the other on one stream (never concurrently): every
     # rank's kernel stores its columns into all four gathered buffers and publishes its arrival; a second layer
-    # then reads the gathered buffer as its input after waiting for the arrivals
+    # then reads the gathered buffer as its input after waiting for the arrivals ("push": the default linear kernels
+    # with the wait in front and the push kernel behind, instead of the one fused launch)
     from atlasinfer_b200 import peer
     world, m, k, n1, n2 = 4, 32, 512, 1024, 512
     w1, w2 = config_weights(n1, k, 61, 0.03), config_weights(n2, n1, 62, 0.03)
@@ -264,10 +267,11 @@ def test_peer_store_gather_with_emulated_ranks(cuda_device):
         for r, arena in enumerate(arenas):
             lo, hi = sharding.row_bounds(n1, world, r, 16)
             lay = atlas_wrappers.build_kernel_layout(sharding.shard_rows(q1, lo, hi).to(cuda_device))
-            layer1.append(peer.GatheredLinear(arena, lay, m, torch.bfloat16, bias=b1[lo:hi].to(cuda_device), poll_limit=4000))
+            layer1.append(peer.GatheredLinear(arena, lay, m, torch.bfloat16, bias=b1[lo:hi].to(cuda_device), poll_limit=4000,
+                                              kernel=kernel))
             lo, hi = sharding.row_bounds(n2, world, r, 16)
             lay = atlas_wrappers.build_kernel_layout(sharding.shard_rows(q2, lo, hi).to(cuda_device))
-            layer2.append(peer.GatheredLinear(arena, lay, m, torch.bfloat16, poll_limit=4000))
+            layer2.append(peer.GatheredLinear(arena, lay, m, torch.bfloat16, poll_limit=4000, kernel=kernel))
         xd = x.to(cuda_device)
         for g in layer1:
             g(xd)                                      # local input: no wait
