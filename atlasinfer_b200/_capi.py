@@ -25,7 +25,7 @@ EXPORTS = (
     "atlas_qlinear_stream_workspace_bytes", "atlas_qlinear_stream", "atlas_qlinear_stream_gather",
     "atlas_peer_wait", "atlas_peer_push", "atlas_peer_alloc", "atlas_peer_free", "atlas_peer_export", "atlas_peer_import",
     "atlas_peer_release",
-    "atlas_qlinear_gemm_workspace_bytes", "atlas_qlinear_gemm",
+    "atlas_qlinear_gemm_workspace_bytes", "atlas_qlinear_gemm", "atlas_qlinear_gemm_gather",
 )
 
 MAX_PEERS = 8
@@ -87,6 +87,8 @@ def load() -> ctypes.CDLL:
     L.atlas_qlinear_stream.argtypes = lin + [vp, sz, vp, vp]
     L.atlas_qlinear_stream_gather.restype = i32
     L.atlas_qlinear_stream_gather.argtypes = lin[:13] + [i64, vp, sz, vp, vp, ctypes.POINTER(PeerGather)]
+    L.atlas_qlinear_gemm_gather.restype = i32
+    L.atlas_qlinear_gemm_gather.argtypes = lin[:13] + [i64, vp, sz, vp, vp, ctypes.POINTER(PeerGather)]
     L.atlas_peer_wait.restype = i32
     L.atlas_peer_wait.argtypes = [vp, i32, vp, i64, vp, vp]
     L.atlas_peer_push.restype = i32

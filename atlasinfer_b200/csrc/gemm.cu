@@ -39,6 +39,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstring>
+
 #include "common.cuh"
 
 namespace atlas {
@@ -212,6 +214,7 @@ struct GemmParams {
     int out_bf16;
     int splits;        // K slices (grid.z); > 1: fp32 partial tiles go to `partials`, a second kernel adds them
     float *partials;   // [splits][m][n_rows] fp32
+    int to_partials;   // write the fp32 tile to `partials` even with one K slice (the second kernel writes y)
     int *error_flag;
 };
 
@@ -521,7 +524,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             const float bv = (p.bias && n < p.n_rows) ? __half2float(__ushort_as_half(__ldg(p.bias + n))) : 0.f;
             // staging tile [BN tokens][128 features (+ pad)] in the idle rings: 16-bit outputs, or fp32
             // partial sums when K is split between CTAs
-            const bool partial = p.splits > 1;
+            const bool partial = p.splits > 1 || p.to_partials;
             unsigned char *stage = base_ptr + OFF_B;
             const int st_bytes = partial ? (GM_BM + 4) * 4 : (GM_BM + 8) * 2;   // row stride; pads keep banks apart
             for (int c = part; c < BN / 32; c += 4) {
@@ -588,32 +591,115 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     }
 }
 
+// Where the second kernel writes y when the output is gathered over the ranks of a node: the same columns of
+// every rank's buffer (plain peer stores), followed by the arrival count (see atlas_qlinear_stream_gather).
+struct FinishGather {
+    int world;   // 0: no gather, y is local
+    int rank;
+    void *y_dst[ATLAS_MAX_PEERS];
+    unsigned int *flags_dst[ATLAS_MAX_PEERS];
+    unsigned int *state;
+};
+
 // Adds the K-slice partial tiles in slice order (deterministic), adds the bias and writes y.
+// VEC: 8 features (16 bytes of output) per thread; needs n_rows % 8 == 0 and 16-byte aligned output rows.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 gemm_finish_kernel(const float *partials, int splits, int m, int n_rows, const uint16_t *bias, void *y, int64_t ldy,
-                   int out_bf16) {
+                   int out_bf16, FinishGather fg) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int64_t total = (int64_t)m * n_rows;
-    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
-        const int row = (int)(i / n_rows), n = (int)(i - (int64_t)row * n_rows);
-        float acc = 0.f;
-        for (int z = 0; z < splits; ++z) acc += partials[(size_t)z * total + i];
-        if (bias) acc += __half2float(__ushort_as_half(__ldg(bias + n)));
-        if (out_bf16) reinterpret_cast<__nv_bfloat16 *>(y)[(int64_t)row * ldy + n] = __float2bfloat16_rn(acc);
-        else reinterpret_cast<__half *>(y)[(int64_t)row * ldy + n] = __float2half_rn(acc);
+    constexpr int W = VEC ? 8 : 1;
+    const int64_t total = (int64_t)m * n_rows, pieces = total / W;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < pieces; i += (int64_t)gridDim.x * 256) {
+        const int64_t e0 = i * W;
+        const int row = (int)(e0 / n_rows), n = (int)(e0 - (int64_t)row * n_rows);
+        float acc[W];
+#pragma unroll
+        for (int e = 0; e < W; ++e) acc[e] = 0.f;
+        for (int z = 0; z < splits; ++z) {
+            const float *src = partials + (size_t)z * total + e0;
+            if (VEC) {
+                const float4 a = __ldcg(reinterpret_cast<const float4 *>(src)), b = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
+                acc[0] += a.x; acc[1 % W] += a.y; acc[2 % W] += a.z; acc[3 % W] += a.w;
+                acc[4 % W] += b.x; acc[5 % W] += b.y; acc[6 % W] += b.z; acc[7 % W] += b.w;
+            } else {
+                acc[0] += __ldcg(src);
+            }
+        }
+        uint16_t out[W];
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+            float v = acc[e];
+            if (bias) v += __half2float(__ushort_as_half(__ldg(bias + n + e)));
+            out[e] = out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+        }
+        const int64_t off = (int64_t)row * ldy + n;
+        const int dests = fg.world > 0 ? fg.world : 1;
+        for (int d = 0; d < dests; ++d) {
+            uint16_t *dst = reinterpret_cast<uint16_t *>(y);
+            if (fg.world > 0) {
+                int to = fg.rank + d;
+                if (to >= fg.world) to -= fg.world;
+                dst = reinterpret_cast<uint16_t *>(fg.y_dst[to]);
+            }
+            if (VEC) *reinterpret_cast<uint4 *>(dst + off) = make_uint4(out[0] | (uint32_t)out[1 % W] << 16, out[2 % W] | (uint32_t)out[3 % W] << 16,
+                                                                        out[4 % W] | (uint32_t)out[5 % W] << 16, out[6 % W] | (uint32_t)out[7 % W] << 16);
+            else dst[off] = out[0];
+        }
+    }
+    if (fg.world > 0) {
+        // the CTA that finishes last tells every rank that this rank's columns are complete
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();   // the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
+            const unsigned int finished = atomicAdd(fg.state, 1u);
+            if (finished == gridDim.x - 1) {
+                __threadfence_system();
+                const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(fg.state + 1) + 1u;
+                fg.state[0] = 0;
+                fg.state[1] = seq;
+                for (int d = 0; d < fg.world; ++d) {
+                    int to = fg.rank + d;
+                    if (to >= fg.world) to -= fg.world;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(fg.flags_dst[to] + fg.rank), "r"(seq) : "memory");
+                }
+            }
+        }
     }
 }
 
-// bf16 -> fp16 (saturating) into a dense [m][k] buffer; also used to make strided fp16 rows dense.
+// bf16 -> fp16 (saturating) into a dense [m][k] buffer; also used to make strided fp16 rows dense.  When x is a
+// gathered buffer that the other ranks fill (`wait_flags`), every CTA first waits, bounded, until all ranks'
+// arrival counts have reached this rank's own (state[1]).
 __global__ void __launch_bounds__(256)
-to_f16_kernel(const uint16_t *x, int64_t ldx, int m, int k, int from_bf16, uint16_t *out) {
+to_f16_kernel(const uint16_t *x, int64_t ldx, int m, int k, int from_bf16, uint16_t *out, const unsigned int *wait_flags,
+              int wait_world, const unsigned int *state, long long poll_limit, int *status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (wait_flags) {
+        if (threadIdx.x < 32) {
+            const int lane = threadIdx.x;
+            const unsigned int target = *reinterpret_cast<const volatile unsigned int *>(state + 1);
+            bool ok = true;
+            if (lane < wait_world) {
+                ok = false;
+                for (long long i = 0; i < poll_limit; ++i) {
+                    unsigned int v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait_flags + lane) : "memory");
+                    if ((int)(v - target) >= 0) { ok = true; break; }
+                    __nanosleep(64);
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok) && lane == 0 && status) atomicExch(status, 1);   // reported; the copy goes on
+        }
+        __syncthreads();
+    }
     const int64_t total = (int64_t)m * (k >> 1);
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
         const int64_t row = i / (k >> 1), c2 = i - row * (k >> 1);
-        uint32_t v = x[row * ldx + 2 * c2] | (uint32_t)x[row * ldx + 2 * c2 + 1] << 16;
+        // (read through L2: with wait_flags the rows were written by other GPUs)
+        uint32_t v = __ldcg(x + row * ldx + 2 * c2) | (uint32_t)__ldcg(x + row * ldx + 2 * c2 + 1) << 16;
         if (from_bf16) {
             float lo = fminf(fmaxf(__uint_as_float(v << 16), -65504.f), 65504.f);
             float hi = fminf(fmaxf(__uint_as_float(v & 0xffff0000u), -65504.f), 65504.f);
@@ -722,14 +808,33 @@ extern "C" size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_rows, 
     return atlas::GM_WS_HEADER + xcopy + part;
 }
 
-extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
-                                  const void *scales_tiled, const int32_t *outlier_chunk_ptr,
-                                  const uint32_t *outlier_entries, const void *outlier_vals_sorted,
-                                  int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y,
-                                  int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
-                                  void *stream) {
-    using namespace atlas;
+namespace atlas {
+namespace {
+
+int gemm_entry(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles, const void *scales_tiled,
+               const int32_t *outlier_chunk_ptr, const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+               int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y, int64_t ldy, void *workspace,
+               size_t workspace_bytes, int32_t *status, void *stream, const AtlasPeerGather *gather) {
     clear_error();
+    FinishGather fg;
+    memset(&fg, 0, sizeof(fg));
+    if (gather) {
+        ATLAS_RETURN_IF(gather->world < 1 || gather->world > ATLAS_MAX_PEERS || gather->rank < 0 || gather->rank >= gather->world ||
+                            !gather->state || gather->poll_limit < 1, ATLAS_ERR_BAD_ARGUMENT,
+                        "atlas_qlinear_gemm_gather: bad gather descriptor");
+        ATLAS_RETURN_IF(m > 64, ATLAS_ERR_UNSUPPORTED,
+                        "atlas_qlinear_gemm_gather: decode-sized batches only (m <= 64); gather larger ones with a collective");
+        fg.world = gather->world;
+        fg.rank = gather->rank;
+        fg.state = gather->state;
+        for (int d = 0; d < gather->world; ++d) {
+            ATLAS_RETURN_IF(!gather->y_dst[d] || !gather->flags_dst[d], ATLAS_ERR_BAD_ARGUMENT,
+                            "atlas_qlinear_gemm_gather: null destination");
+            fg.y_dst[d] = gather->y_dst[d];
+            fg.flags_dst[d] = gather->flags_dst[d];
+        }
+        y = gather->y_dst[gather->rank];
+    }
     ATLAS_RETURN_IF(!x || !tiles || !scales_tiled || !outlier_chunk_ptr || !y || !workspace, ATLAS_ERR_BAD_ARGUMENT,
                     "atlas_qlinear_gemm: null buffer");
     ATLAS_RETURN_IF(m < 0 || n_rows <= 0 || n_cols <= 0 || ldx < n_cols || ldy < n_rows, ATLAS_ERR_BAD_ARGUMENT,
@@ -757,14 +862,17 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
     const void *xb = x;
     int64_t ldb = ldx;
     const size_t xcopy = ((size_t)m * (size_t)n_cols * 2 + 255) & ~(size_t)255;
-    const bool direct = dtype == ATLAS_DTYPE_F16 && ((uintptr_t)x & 15) == 0 && (ldx % 8) == 0;
+    const unsigned int *wait_flags = gather ? gather->wait_flags : nullptr;   // the wait lives in the copy kernel
+    const bool direct = dtype == ATLAS_DTYPE_F16 && ((uintptr_t)x & 15) == 0 && (ldx % 8) == 0 && !wait_flags;
     if (!direct) {
         uint16_t *xf = (uint16_t *)((char *)workspace + GM_WS_HEADER);
         const int64_t pairs = m * (n_cols / 2);
         const int64_t blocks = ceil_div_i64(pairs, 256);
         cudaLaunchConfig_t cfg = pdl_config(dim3((unsigned)(blocks < 65535 ? blocks : 65535)), dim3(256), 0, st);
         rc = check_cuda(cudaLaunchKernelEx(&cfg, to_f16_kernel, (const uint16_t *)x, ldx, (int)m, (int)n_cols,
-                                           (int)(dtype == ATLAS_DTYPE_BF16), xf), "to_f16_kernel launch");
+                                           (int)(dtype == ATLAS_DTYPE_BF16), xf, wait_flags, gather ? (int)gather->world : 0,
+                                           gather ? (const unsigned int *)gather->state : (const unsigned int *)nullptr,
+                                           gather ? (long long)gather->poll_limit : 0ll, (int *)status), "to_f16_kernel launch");
         if (rc) return rc;
         xb = xf;
         ldb = n_cols;
@@ -813,6 +921,7 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
     p.out_bf16 = dtype == ATLAS_DTYPE_BF16;
     p.splits = gemm_splits_for(m, n_rows, n_cols, gemm_sm_count());
     p.partials = (float *)((char *)workspace + GM_WS_HEADER + xcopy);
+    p.to_partials = gather != nullptr;   // the gather is the second kernel's job
     p.error_flag = status;
     switch (bn) {
         case 32: rc = launch_gemm<32>(x_map, c_map, p, st); break;
@@ -821,12 +930,42 @@ extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t l
         default: rc = launch_gemm<256>(x_map, c_map, p, st); break;
     }
     if (rc) return rc;
-    if (p.splits > 1) {
-        const int64_t total = m * n_rows;
-        const int64_t blocks = ceil_div_i64(total, 256);
+    if (p.splits > 1 || p.to_partials) {
+        const bool vec = n_rows % 8 == 0 && ldy % 8 == 0 && (((uintptr_t)y & 15) == 0) &&
+                         (((uintptr_t)p.partials & 15) == 0);
+        bool vec_all = vec;
+        for (int d = 0; d < fg.world; ++d) vec_all = vec_all && (((uintptr_t)fg.y_dst[d] & 15) == 0);
+        const int64_t pieces = m * n_rows / (vec_all ? 8 : 1);
+        const int64_t blocks = ceil_div_i64(pieces, 256);
         cudaLaunchConfig_t cfg = pdl_config(dim3((unsigned)(blocks < 2048 ? blocks : 2048)), dim3(256), 0, st);
-        rc = check_cuda(cudaLaunchKernelEx(&cfg, gemm_finish_kernel, (const float *)p.partials, p.splits, (int)m, (int)n_rows,
-                                           (const uint16_t *)bias, y, ldy, p.out_bf16), "gemm_finish_kernel launch");
+        auto kern = vec_all ? gemm_finish_kernel<true> : gemm_finish_kernel<false>;
+        rc = check_cuda(cudaLaunchKernelEx(&cfg, kern, (const float *)p.partials, p.splits, (int)m, (int)n_rows,
+                                           (const uint16_t *)bias, y, ldy, p.out_bf16, fg), "gemm_finish_kernel launch");
     }
     return rc;
+}
+
+}  // namespace
+}  // namespace atlas
+
+extern "C" int atlas_qlinear_gemm(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
+                                  const void *scales_tiled, const int32_t *outlier_chunk_ptr,
+                                  const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+                                  int64_t n_rows, int64_t n_cols, int block_size, const void *bias, void *y,
+                                  int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
+                                  void *stream) {
+    ATLAS_RETURN_IF(!y, ATLAS_ERR_BAD_ARGUMENT, "atlas_qlinear_gemm: null buffer");
+    return atlas::gemm_entry(x, dtype, m, ldx, tiles, scales_tiled, outlier_chunk_ptr, outlier_entries, outlier_vals_sorted,
+                             n_rows, n_cols, block_size, bias, y, ldy, workspace, workspace_bytes, status, stream, nullptr);
+}
+
+extern "C" int atlas_qlinear_gemm_gather(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
+                                         const void *scales_tiled, const int32_t *outlier_chunk_ptr,
+                                         const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+                                         int64_t n_rows, int64_t n_cols, int block_size, const void *bias,
+                                         int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
+                                         void *stream, const AtlasPeerGather *gather) {
+    ATLAS_RETURN_IF(!gather, ATLAS_ERR_BAD_ARGUMENT, "atlas_qlinear_gemm_gather: null gather descriptor");
+    return atlas::gemm_entry(x, dtype, m, ldx, tiles, scales_tiled, outlier_chunk_ptr, outlier_entries, outlier_vals_sorted,
+                             n_rows, n_cols, block_size, bias, nullptr, ldy, workspace, workspace_bytes, status, stream, gather);
 }

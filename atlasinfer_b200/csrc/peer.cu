@@ -70,10 +70,9 @@ __global__ void __launch_bounds__(256) peer_push_kernel(PushParams p) {
                 if (off[u] >= 0) *reinterpret_cast<T *>(p.dst[to] + off[u]) = v[u];
         }
     }
-    __threadfence_system();   // this thread's stores into the other ranks' buffers are out
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
+        __threadfence_system();   // the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
         const unsigned int finished = atomicAdd(p.state, 1u);
         if (finished == gridDim.x - 1) {
             __threadfence_system();

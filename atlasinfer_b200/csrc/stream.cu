@@ -726,11 +726,10 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
         }
     }
 
-    if (p.world > 1) __threadfence_system();   // this thread's stores into the other ranks' buffers are out
     __syncthreads();
     if (p.world > 1 && tid == 0) {
         // the CTA that finishes last tells every rank that this rank's shard of the output is complete
-        __threadfence_system();
+        __threadfence_system();   // the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
         const unsigned int finished = atomicAdd(p.state, 1u);
         if (finished == (unsigned int)grid - 1) {
             __threadfence_system();

@@ -7,8 +7,9 @@ straight into every rank's gathered [m, N] buffer over NVLink and then publishes
 kernel that consumes the buffer waits (bounded) until all ranks have arrived.  The shards are 64 KB - 1.8 MB,
 so what this removes is the collective's launch and synchronisation latency, per linear.  The stores are either
 the epilogue of the streaming linear kernel (``kernel="stream"``: one launch does the linear, the wait and the
-gather) or a small push kernel behind the default linear kernels (``kernel="push"``: the per-strip kernel up to
-16 rows of x, the tcgen05 kernel above), with the wait as a kernel of its own in front.
+gather), part of the tcgen05 path (``kernel="gemm"``, up to 64 rows of x: its fp16 copy kernel waits, the kernel
+that adds the K slices stores to every rank; no extra launch), or a small push kernel behind the default linear
+kernels (``kernel="push"``: any number of rows), with the wait as a kernel of its own in front.
 
 One process per GPU of one node.  ``PeerArena`` owns the memory the ranks share: each rank allocates an arena
 of the same size (``atlas_peer_alloc``: plain cudaMalloc memory), the ranks exchange CUDA IPC handles through
@@ -126,7 +127,7 @@ class GatheredLinear:
 
     def __init__(self, arena: PeerArena, layout: aw.KernelLayout, m_max: int, dtype: torch.dtype,
                  bias: Optional[torch.Tensor] = None, poll_limit: int = DEFAULT_POLL_LIMIT, kernel: str = "stream"):
-        if kernel not in ("stream", "push"):
+        if kernel not in ("stream", "gemm", "push"):
             raise ValueError(f"kernel={kernel!r}")
         self.kernel = kernel
         self.arena = arena
@@ -168,11 +169,26 @@ class GatheredLinear:
                                        ctypes.byref(self._desc), _capi.stream_ptr(dev))
             _capi.check(st, "atlas_peer_push")
             return self.out[:m]
+        dtype = _capi.DTYPE_F16 if x.dtype == torch.float16 else _capi.DTYPE_BF16
+        desc = self._desc_wait if wait else self._desc
+        if self.kernel == "gemm":
+            if m > self.m_max or m > 64:
+                raise ValueError(f"{m} rows of x; this gathered linear was set up for {min(self.m_max, 64)}")
+            if m == 0:
+                return self.out[:0]
+            ws_bytes = int(L.atlas_qlinear_gemm_workspace_bytes(m, lay.n_rows, lay.n_cols))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            with torch.cuda.device(dev):
+                st = L.atlas_qlinear_gemm_gather(
+                    x2.data_ptr(), dtype, m, x2.stride(0) if m > 1 else lay.n_cols, lay.tiles.data_ptr(),
+                    lay.scales_tiled.data_ptr(), lay.chunk_ptr.data_ptr(), _capi.ptr(lay.entries), _capi.ptr(lay.vals_sorted),
+                    lay.n_rows, lay.n_cols, lay.block_size, _capi.ptr(self.bias), self.width, ws.data_ptr(), ws_bytes,
+                    aw.status_word(dev).data_ptr(), _capi.stream_ptr(dev), ctypes.byref(desc))
+            _capi.check(st, "atlas_qlinear_gemm_gather")
+            return self.out[:m]
         if m > self.m_max or m > aw.STREAM_MAX_ROWS:
             raise ValueError(f"{m} rows of x; this gathered linear was set up for {min(self.m_max, aw.STREAM_MAX_ROWS)}")
-        dtype = _capi.DTYPE_F16 if x.dtype == torch.float16 else _capi.DTYPE_BF16
         ws = aw.stream_workspace(dev)
-        desc = self._desc_wait if wait else self._desc
         with torch.cuda.device(dev):
             st = L.atlas_qlinear_stream_gather(
                 x2.data_ptr(), dtype, m, x2.stride(0) if m > 1 else lay.n_cols, lay.tiles.data_ptr(),

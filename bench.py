@@ -392,8 +392,8 @@ def measure_tp70b(rank, world, steps, warmup, barrier):
     Every rank owns rows [r*N/g, (r+1)*N/g) of each linear (8 distinct layers, cycled ten times to stand for the
     80 layers; one layer's shards already exceed L2), q/k/v and gate/up fused into one launch each, and the
     [32, N/g] output shards are all-gathered after every launch: by NCCL (`nccl_allgather`), or by the ranks'
-    own peer stores into symmetric buffers followed by a flag exchange (`peer_stores_fused`: in the streaming
-    linear kernel's epilogue; `peer_push`: a push kernel behind the default linear kernels; see
+    own peer stores into symmetric buffers followed by a flag exchange (`peer_stores_stream`: in the streaming
+    linear kernel's epilogue; `peer_stores_gemm`: in the tcgen05 path's second kernel; `peer_push`: a push kernel behind the default linear kernels; see
     atlasinfer_b200/peer.py).  Returns ms per token for each, the weight-streaming-only time and the aggregate
     algorithmic GB/s."""
     import torch.distributed as dist
@@ -435,7 +435,7 @@ def measure_tp70b(rank, world, steps, warmup, barrier):
         out[name] = dict(ms_per_token=secs / steps * 1e3, launch=mode)
     # the ranks' own peer stores instead of the collective: fused into the streaming linear kernel, or as a push
     # kernel behind the default linear kernels (at one rank: the same launches, stores to the own buffer only)
-    for name, kernel in (("peer_stores_fused", "stream"), ("peer_push", "push")):
+    for name, kernel in (("peer_stores_stream", "stream"), ("peer_stores_gemm", "gemm"), ("peer_push", "push")):
         try:
             out[name] = measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, rank, world, dev, kernel)
         except Exception as e:  # noqa: BLE001 - keep the other figures

@@ -266,6 +266,18 @@ ATLAS_API int atlas_qlinear_stream_gather(const void *x, int dtype, int64_t m, i
                                           int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
                                           void *stream, const AtlasPeerGather *gather);
 
+/* The same gather behind the tcgen05 path of atlas_qlinear_gemm, for m <= 64:
+ * the kernel that adds the K-slice partial tiles writes y into every rank's
+ * buffer and publishes the arrival; with `wait_flags` the kernel that copies x
+ * to fp16 waits first (bounded).  No extra launch.  `workspace` as for
+ * atlas_qlinear_gemm. */
+ATLAS_API int atlas_qlinear_gemm_gather(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *tiles,
+                                        const void *scales_tiled, const int32_t *outlier_chunk_ptr,
+                                        const uint32_t *outlier_entries, const void *outlier_vals_sorted,
+                                        int64_t n_rows, int64_t n_cols, int block_size, const void *bias,
+                                        int64_t ldy, void *workspace, size_t workspace_bytes, int32_t *status,
+                                        void *stream, const AtlasPeerGather *gather);
+
 /* Waits (one small kernel on `stream`) until all `world` entries of `flags`
  * have reached the count in state[1]; sets *status non-zero if `poll_limit`
  * polls were not enough.  For consumers of a gathered buffer that are not

@@ -247,7 +247,7 @@ def _arena_u32(arena, offset, count):
     return arena.local_tensor(offset, (count,), torch.int32)
 
 
-@pytest.mark.parametrize("kernel", ["stream", "push"])
+@pytest.mark.parametrize("kernel", ["stream", "gemm", "push"])
 def test_peer_store_gather_with_emulated_ranks(kernel, cuda_device):
     # four "ranks" in this process on one GPU, run one after the other on one stream (never concurrently): every
     # rank's kernel stores its columns into all four gathered buffers and publishes its arrival; a second layer
