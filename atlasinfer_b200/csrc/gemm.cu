@@ -54,7 +54,7 @@ constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
 constexpr int GM_BK = 64;   // K per pipeline step (one 128-byte swizzle row of fp16)
 constexpr int GM_SK = 2;    // k-tiles per pipeline stage: one barrier round trip, poll and commit per 128 columns of K
 constexpr int GM_XS = 2;    // activation ring depth, in stages
-constexpr int GM_CS = 4;    // code ring depth, in stages
+// (the code ring depth depends on the token tile: Smem<BN>::CS)
 constexpr int GM_PH = 4;    // K-stage phases of the dequantizers = `ready` / `mma_done` barriers
 constexpr int GM_A_COLS = GM_SK * GM_BK / 2;     // TMEM columns of one A stage: two fp16 per 32-bit cell
 constexpr uint32_t C_BYTES = GM_BM * GM_BK;      // 8 KB code tile
@@ -63,17 +63,22 @@ constexpr uint32_t S_BYTES = 256;                // one scale block: 128 rows x 
 template <int BN>
 struct Smem {
     static constexpr uint32_t B_BYTES = BN * GM_BK * 2;   // fp16 activation tile of one k-tile
+    // Code ring depth, in stages of GM_SK k-tiles (16 KB): the bytes an SM keeps in flight.  Decode-sized token
+    // tiles are HBM-bound and leave the room for a deep ring (160 KB in flight covers ~3 us of loaded DRAM latency
+    // at an SM's share of the bandwidth); the 256-token tile is compute-bound and needs the room for activations.
+    static constexpr int CS = BN <= 32 ? 10 : (BN == 64 ? 8 : (BN == 128 ? 6 : 4));
     static constexpr uint32_t OFF_B = 0;
     static constexpr uint32_t OFF_C = OFF_B + GM_XS * GM_SK * B_BYTES;
-    static constexpr uint32_t OFF_BAR = OFF_C + GM_CS * GM_SK * C_BYTES;
+    static constexpr uint32_t OFF_BAR = OFF_C + CS * GM_SK * C_BYTES;
     static constexpr uint32_t OFF_S = OFF_BAR + 256;
-    static constexpr uint32_t TOTAL = OFF_S + GM_CS * GM_SK * S_BYTES + 1024 /*alignment slack*/;
+    static constexpr uint32_t TOTAL = OFF_S + CS * GM_SK * S_BYTES + 1024 /*alignment slack*/;
     // A stages in tensor memory (64 columns each) beside the accumulator columns [0, BN); allocations are powers of two
     static constexpr int A_STAGES = BN == 256 ? 4 : 2;
     static constexpr uint32_t TMEM_COLS = BN + A_STAGES * GM_A_COLS <= 256 ? 256 : 512;
     static_assert(BN + A_STAGES * GM_A_COLS <= 512, "tensor memory");
     // the epilogue stages the output tile over the (then idle) activation and code rings
-    static_assert((BN * (GM_BM + 4)) * 4 <= GM_XS * GM_SK * B_BYTES + GM_CS * GM_SK * C_BYTES, "epilogue staging does not fit");
+    static_assert((BN * (GM_BM + 4)) * 4 <= GM_XS * GM_SK * B_BYTES + CS * GM_SK * C_BYTES, "epilogue staging does not fit");
+    static_assert(TOTAL <= 227 * 1024, "shared memory");
 };
 constexpr int GM_SPIN_LIMIT = 1 << 20;       // polls per wait
 
@@ -236,8 +241,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     auto ready_bar = [&](int s) { return bars + 8u * s; };
     auto mma_done = [&](int s) { return bars + 8u * (GM_PH + s); };
     auto full_c = [&](int s) { return bars + 8u * (2 * GM_PH + s); };
-    auto empty_c = [&](int s) { return bars + 8u * (2 * GM_PH + GM_CS + s); };
-    constexpr int N_BARS = 2 * GM_PH + 2 * GM_CS + 1;
+    constexpr int CS = SM::CS;
+    auto empty_c = [&](int s) { return bars + 8u * (2 * GM_PH + CS + s); };
+    constexpr int N_BARS = 2 * GM_PH + 2 * CS + 1;
     static_assert(N_BARS * 8 + 16 <= 256, "barrier area");
     const uint32_t accfull_bar = bars + 8u * (N_BARS - 1);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + OFF_BAR + 8 * N_BARS);
@@ -252,7 +258,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     const int KT = (int)((long long)p.k_tiles * (blockIdx.z + 1) / p.splits) - kt_begin;
     const int NST = (KT + GM_SK - 1) / GM_SK;   // pipeline stages of GM_SK k-tiles (the last one may hold a single k-tile)
     // stage st uses barriers ready[st % 4] / mma_done[st % 4] in round st / 4, activation slot st % GM_XS, code slot
-    // st % GM_CS and A stage st % AS; a resource used by stage st is free again when mma_done of stage st fired
+    // st % CS and A stage st % AS; a resource used by stage st is free again when mma_done of stage st fired
     auto done_bar_of = [&](int st) { return mma_done(st % GM_PH); };
     auto done_par_of = [&](int st) { return (uint32_t)((st / GM_PH) & 1); };
 
@@ -264,7 +270,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             mbar_init(ready_bar(s), 4 * 32 + 1);
             mbar_init(mma_done(s), 1);
         }
-        for (int s = 0; s < GM_CS; ++s) {
+        for (int s = 0; s < CS; ++s) {
             mbar_init(full_c(s), 1);
             mbar_init(empty_c(s), 4);
         }
@@ -304,7 +310,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             const int64_t crow0 = (int64_t)blockIdx.x * p.k_tiles + kt_begin;   // code tiles are rows of 128 in the map
             const int bpr = p.n_cols / p.bs;
             for (int st = 0; st < NST; ++st) {
-                const int slot = st % GM_CS, round = st / GM_CS;
+                const int slot = st % CS, round = st / CS;
                 if (round > 0 && !mbar_wait<200>(empty_c(slot), (round - 1) & 1)) { *s_abort = 1; break; }
                 if (*s_abort) break;
                 const int nk = min(GM_SK, KT - st * GM_SK);
@@ -434,7 +440,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             }
             const uint32_t second = __ballot_sync(0xffffffffu, (pk0 >> 22) & 1u);   // entries of the stage's second k-tile
 
-            const int sc_ = st % GM_CS, cround = st / GM_CS;   // code slot
+            const int sc_ = st % CS, cround = st / CS;   // code slot
             if (!mbar_wait_warp<40>(full_c(sc_), cround & 1, s_abort)) { ok = false; break; }
 #pragma unroll
             for (int j = 0; j < GM_SK; ++j) {
@@ -758,15 +764,22 @@ cudaLaunchConfig_t pdl_config(dim3 grid, dim3 block, size_t smem, cudaStream_t s
 // tokens per tile for a batch of m rows
 int gemm_bn_for(int64_t m) { return m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
 
-// K slices: enough CTAs to occupy the SMs when the output has few tiles (decode-sized batches only)
+// K slices for decode-sized batches (one CTA per SM, `tiles` output tiles): the count that minimises
+// waves x (k-tiles per CTA + the fixed cost of a CTA, about 12 k-tiles' worth of streaming), so that neither a
+// nearly empty last wave nor many short CTAs dominate.
 int gemm_splits_for(int64_t m, int64_t n_rows, int64_t n_cols, int sms) {
     const int bn = gemm_bn_for(m);
     if (bn > 64) return 1;
     const int64_t tiles = ceil_div_i64(n_rows, GM_BM) * ceil_div_i64(m, bn);
-    int splits = 1;
     const int k_tiles = (int)(n_cols / 64);
-    while (splits < 8 && tiles * splits < sms && k_tiles / (splits * 2) >= 8) splits *= 2;
-    return splits;
+    int best = 1;
+    int64_t best_cost = 0;
+    for (int s = 1; s <= 8; s *= 2) {
+        if (s > 1 && k_tiles / s < 8) break;
+        const int64_t cost = ceil_div_i64(tiles * s, sms) * (ceil_div_i64(k_tiles, s) + 12);
+        if (s == 1 || cost < best_cost) { best = s; best_cost = cost; }
+    }
+    return best;
 }
 
 int gemm_sm_count() {

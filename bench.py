@@ -697,7 +697,7 @@ def run_ours(args, rank, world, local_rank):
                           traffic=NCU_DRAM_BYTES_PER_WEIGHT * n_weights / launches,
                           traffic_unit="bytes per launch", algorithmic_bytes_per_launch=nbytes / launches,
                           avg_launch_us=secs / args.steps / launches * 1e6,
-                          peak_source=pk["source"], kernel="qlinear_stream_kernel",
+                          peak_source=pk["source"], kernel="gemv_strip_kernel",
                           frac_of_nominal_8tbs=per_gpu / 8000.0),
             cpu_baseline=cpu, extra=extra, setup_s=t_setup)
         print(json.dumps(line), flush=True)
