@@ -82,15 +82,46 @@ __device__ __forceinline__ int64_t tile_offset(int64_t row, int64_t col, int64_t
     return ((((rt * k_tiles + kt) * 8 + strip) * 2 + h) * 32 + (g * 4 + tig)) * 16 + byte;
 }
 
+// One thread per 16 consecutive columns of a row = one 16-byte unit of the tile-major layout (n_cols is a multiple
+// of 64, so a unit never straddles rows, and a span of DQ_SPAN positions is DQ_SPAN / 16 whole units).  The thread
+// finds how many outliers precede its unit (binary search in the span's short window of the sorted index list),
+// walks its 16 positions against the list and the compacted code stream, and stores the unit at once.
 __global__ void __launch_bounds__(DQ_THREADS)
 repack_kernel(const int8_t *codes, int64_t n_codes, const int64_t *oidx, int64_t n_out, int64_t n_rows,
               int64_t n_cols, uint8_t *tiles) {
-    const int64_t k_tiles = n_cols >> 6;
-    walk_span(codes, n_codes, oidx, n_out, n_rows * n_cols, [&](int64_t p, bool is_out, int64_t k, int8_t code) {
-        const int64_t row = p / n_cols, col = p - row * n_cols;
-        tiles[tile_offset(row, col, k_tiles)] = (uint8_t)((int)code + 128);
-        (void)is_out; (void)k;
-    });
+    static_assert(DQ_SPAN == DQ_THREADS * 16, "one 16-byte unit per thread");
+    __shared__ int64_t s_lo, s_hi;
+    const int64_t numel = n_rows * n_cols;
+    const int64_t span0 = (int64_t)blockIdx.x * DQ_SPAN;
+    const int64_t span1 = min(span0 + DQ_SPAN, numel);
+    if (threadIdx.x == 0) s_lo = lower_bound_i64(oidx, n_out, span0);
+    if (threadIdx.x == 32) s_hi = lower_bound_i64(oidx, n_out, span1);
+    __syncthreads();
+    const int64_t p0 = span0 + (int64_t)threadIdx.x * 16;
+    if (p0 >= span1) return;
+    int64_t a = s_lo, b = s_hi;
+    const int64_t hi = b;
+    while (a < b) {
+        const int64_t mid = (a + b) >> 1;
+        if (oidx[mid] < p0) a = mid + 1; else b = mid;
+    }
+    int64_t next_out = a < hi ? oidx[a] : numel;   // the next outlier position at or after p0 (numel: none in this span)
+    int64_t ci = p0 - a;                            // position of p0's code in the compacted stream
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        uint32_t byte = 128u;                       // an outlier's place holds code 0
+        if (p0 + j == next_out) {
+            ++a;
+            next_out = a < hi ? oidx[a] : numel;
+        } else {
+            if (ci < n_codes) byte = (uint32_t)((int)codes[ci] + 128);
+            ++ci;
+        }
+        w[j >> 2] |= byte << (8 * (j & 3));
+    }
+    const int64_t row = p0 / n_cols, col = p0 - row * n_cols;
+    *reinterpret_cast<uint4 *>(tiles + tile_offset(row, col, n_cols >> 6)) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // Rows beyond n_rows inside the last 128-row tile: code 0.
@@ -231,6 +262,7 @@ int atlas_repack(const int8_t *codes, int64_t n_codes, const void *outlier_vals,
                         (n_codes && !codes) ||
                         (n_outliers && (!outlier_idx || !outlier_vals || !outlier_entries || !outlier_vals_sorted)),
                     ATLAS_ERR_BAD_ARGUMENT, "atlas_repack: null buffer");
+    ATLAS_RETURN_IF(((uintptr_t)tiles & 15) != 0, ATLAS_ERR_BAD_ARGUMENT, "atlas_repack: tiles must be 16-byte aligned");
     int rc = check_device();
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;

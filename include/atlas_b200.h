@@ -131,7 +131,7 @@ ATLAS_API int atlas_dequantize(const int8_t *codes, int64_t n_codes, const void 
  *                    uint8 (outlier positions hold 128, i.e. code 0), ordered
  *                    [row/128][col/64][row%128][col%64] (every 128-row x
  *                    64-column tile is a contiguous 8 KB matrix of 64-byte
- *                    rows); rows padded to a multiple of 128
+ *                    rows); rows padded to a multiple of 128; 16-byte aligned
  *   scales_tiled     atlas_tiles_bytes / block_size fp16: the scales ordered
  *                    [row/128][block][row%128] (0 for padding rows)
  *   outlier_row_ptr  n_rows + 1 int32: CSR row starts into the canonical
