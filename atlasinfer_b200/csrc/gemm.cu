@@ -522,7 +522,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
 
         // epilogue: TMEM lane = output feature, column = token.  The accumulators go through shared
         // memory (the rings are idle by now) so that y is written in 16-byte pieces along a token row.
-        if (mbar_wait_warp<200>(accfull_bar, 0, s_abort)) {
+        // The 16 warps take ONE decision together (a barrier that ANDs their votes): the named barrier inside the
+        // epilogue must be reached by all of them or by none, also when only some saw a wait run out.
+        const bool acc_ok = mbar_wait_warp<200>(accfull_bar, 0, s_abort);
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.u32 p, %1, 0;\n\t"
+            "barrier.cta.red.and.pred q, 1, %2, p;\n\t"
+            "selp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(all_ok) : "r"((uint32_t)acc_ok), "n"(GM_EPI_WARPS * 32) : "memory");
+        if (all_ok) {
             tcgen05_fence_after();
             const int part = (warp - GM_CTRL_WARPS) >> 2;   // four warps share a TMEM lane quarter: 32-column chunks part, part + 4, ..
             const int nl = q * 32 + lane;                   // feature inside the tile

@@ -59,7 +59,13 @@ def status_word(dev: torch.device) -> torch.Tensor:
 
 
 def check_status(dev: torch.device) -> None:
-    """Synchronise and raise if any kernel on ``dev`` reported a timed-out wait."""
+    """Synchronise and raise if any kernel on ``dev`` reported a timed-out wait.
+
+    The linear kernels never stall the host: a bounded wait that runs out inside a kernel (a copy that never
+    lands, a peer that never arrives) sets a per-device status word and the kernel finishes on what it has.
+    ``QuantizedLinear.forward`` does not read the word (that would synchronise every call); a caller that wants
+    the check calls this where a synchronisation is acceptable, e.g. once per generated token or per batch.
+    The word is cleared when the error is raised."""
     if int(status_word(dev).item()) != 0:
         status_word(dev).zero_()
         raise _capi.AtlasError(_capi.ERR_TIMEOUT, "a quantized-linear kernel gave up on a bounded wait")

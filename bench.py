@@ -18,11 +18,13 @@ offload_canonical), so a step is 4 launches per layer, 128 in all.
             activations from pinned host memory to the device, replays the
             graph and copies all 224 outputs back to pinned host memory, inside
             the timed region
-  extra     the same pass without fusing (224 launches), batch 4 / 16 / 32,
-            prefill GEMM TFLOP/s, quantize GB/s, the OPT-1.3B-architecture model
-            end to end (quantize seconds, greedy decode tokens/s) and the
-            70B-shaped column-parallel decode (batch 32) at this N, with the
-            NCCL all-gather and with the kernels' own peer stores
+  extra     the 70B-shaped column-parallel decode (batch 32) at this N, with the
+            NCCL all-gather and with the kernels' own peer stores, and the
+            layer-sharded quantization; in the single-GPU run also the figures
+            that do not depend on N: the same pass without fusing (224
+            launches), batch 4 / 16 / 32, prefill GEMM TFLOP/s, quantize GB/s,
+            the OPT-1.3B-architecture model end to end (quantize seconds,
+            greedy decode tokens/s)
 
 With --gpus N > 1 every rank runs the headline pass on its own GPU (replicas, no
 collective: the path shards by independent tensors) and `value` is the sum over
@@ -386,7 +388,7 @@ def measure_opt13b():
     return res
 
 
-def measure_tp70b(rank, world, steps, warmup, barrier):
+def measure_tp70b(rank, world, steps, warmup, barrier, all_forms=False):
     """Config 5: Llama-3-70B-shaped decode, batch 32, column-parallel over `world` ranks.
 
     Every rank owns rows [r*N/g, (r+1)*N/g) of each linear (8 distinct layers, cycled ten times to stand for the
@@ -435,7 +437,10 @@ def measure_tp70b(rank, world, steps, warmup, barrier):
         out[name] = dict(ms_per_token=secs / steps * 1e3, launch=mode)
     # the ranks' own peer stores instead of the collective: fused into the streaming linear kernel, or as a push
     # kernel behind the default linear kernels (at one rank: the same launches, stores to the own buffer only)
-    for name, kernel in (("peer_stores_stream", "stream"), ("peer_stores_gemm", "gemm"), ("peer_push", "push")):
+    forms = [("peer_stores_gemm", "gemm")]
+    if all_forms:
+        forms += [("peer_stores_stream", "stream"), ("peer_push", "push")]
+    for name, kernel in forms:
         try:
             out[name] = measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, rank, world, dev, kernel)
         except Exception as e:  # noqa: BLE001 - keep the other figures
@@ -485,7 +490,12 @@ def measure_tp_peer_stores(launches, xs, m, reps, steps, warmup, barrier, rank, 
         with torch.cuda.graph(graph):
             one_pass()
         secs = allmax(time_steps(graph.replay, steps, warmup, barrier), world, dev)
-        aw.check_status(dev)
+        # a wait that ran out on ANY rank fails the measurement on EVERY rank (the ranks must stay in step for
+        # the collectives that follow)
+        bad = float(aw.status_word(dev).item() != 0)
+        aw.status_word(dev).zero_()
+        if allmax(bad, world, dev) > 0:
+            return dict(error="a bounded wait on the other ranks' arrivals ran out")
         return dict(ms_per_token=secs / steps * 1e3, launch="graph")
     finally:
         arena.close()
@@ -596,6 +606,16 @@ def run_reference(args, rank, world):
 NCU_DRAM_BYTES_PER_WEIGHT = 1.052   # dram__bytes_read.sum + dram__bytes_write.sum per weight over one layer's four fused launches (ncu capture)
 
 
+_T0 = time.perf_counter()
+PG_TIMEOUT = __import__("datetime").timedelta(seconds=180)   # a rank out of step ends the run in minutes, not in ten
+
+
+def progress(rank, what):
+    """One line per finished phase on stderr (rank 0), so a slow or stuck phase can be told from the log."""
+    if rank == 0:
+        print(f"[bench +{time.perf_counter() - _T0:6.1f}s] {what}", file=sys.stderr, flush=True)
+
+
 def workload_config(m, layers):
     return dict(workload="llama2-7b decode linears: 32 layers x (q,k,v,o 4096x4096; gate,up 11008x4096; "
                          "down 4096x11008), block 128, z 3.0, weights N(0,0.02)+0.1% outliers",
@@ -611,7 +631,7 @@ def run_ours(args, rank, world, local_rank):
     _capi.load()  # fail here, loudly, if the CUDA library is missing
     barrier = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=PG_TIMEOUT)
         barrier = dist.barrier
     pk = peaks()
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -632,15 +652,18 @@ def run_ours(args, rank, world, local_rank):
     per_gpu = value / world
     n_weights = sum(n * k for l in model for n, k, _ in l.stats.values())
 
+    progress(rank, f"headline and end-to-end passes done ({value:.0f} / {e2e_value:.0f} GB/s)")
     extra = dict(resident_bytes_per_weight=resident / n_weights)
     half = max(2, args.steps // 2)
-    if rank == 0 and not args.headline_only:
+    # figures that do not depend on the number of ranks are taken in the single-GPU run only
+    single = world == 1 and not args.headline_only
+    if single:
         for m in (4, 16, 32):
             b, s, _ = measure_gemv(model, m, half, 3)
             extra[f"decode_m{m}_gbs"] = b * half / s / 1e9
     del model
     torch.cuda.empty_cache()
-    if rank == 0 and not args.headline_only and not args.no_fuse:
+    if single and not args.no_fuse:
         unfused = build_model(LLAMA7B_LINEARS, args.layers, torch.Generator(device=dev).manual_seed(99), 0.02, fuse=False)
         b, s, ln = measure_gemv(unfused, 1, half, 3)
         extra["unfused_gbs"] = b * half / s / 1e9
@@ -649,14 +672,15 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.empty_cache()
     if not args.headline_only:
         try:
-            tp = measure_tp70b(rank, world, max(2, args.steps // 5), 3, barrier)
+            tp = measure_tp70b(rank, world, max(2, args.steps // 5), 3, barrier, args.all_gather_forms)
             qs = measure_quantize_sharded(rank, world, 2, 1, barrier)
             if rank == 0:
                 extra["tp70b_decode"] = tp
                 extra["quantize_layer_sharded_gbs"] = qs
         except Exception as e:  # noqa: BLE001 - keep the headline line
             extra["tp70b_error"] = repr(e)
-    if rank == 0 and not args.headline_only:
+        progress(rank, "70B-shaped column-parallel decode and layer-sharded quantization done")
+    if single:
         quarter = max(2, args.steps // 4)
         for name, fn in (("prefill_gemm_tflops", lambda: measure_gemm(quarter, 3)),
                          ("quantize_gbs", lambda: dict(zip(("batched", "one_by_one"), measure_quantize(quarter, 3)))),
@@ -717,6 +741,9 @@ def main():
     ap.add_argument("--no-fuse", action="store_true", help="one launch per linear (224 per step) instead of 4 per layer")
     ap.add_argument("--layers", type=int, default=LLAMA7B["layers"],
                     help="decoder layers in the pass (default: the full 32; smaller only for profiler captures)")
+    ap.add_argument("--all-gather-forms", action="store_true",
+                    help="70B-shaped decode: also time the gather fused into the streaming kernel and the push kernel "
+                         "(default: NCCL all-gather and the peer stores of the tcgen05 path)")
     ap.add_argument("--no-graph", action="store_true", help="launch the pass directly instead of replaying a graph")
     ap.add_argument("--only", default=None, choices=["gemm", "quantize", "opt13b", "tp70b"],
                     help="run just one of the secondary measurements and print it (for profiler captures)")
@@ -740,9 +767,9 @@ def main():
             barrier = None
             if world > 1:
                 import torch.distributed as dist
-                dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+                dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=PG_TIMEOUT)
                 barrier = dist.barrier
-            out = {"tp70b_decode": measure_tp70b(rank, world, args.steps, args.warmup, barrier)}
+            out = {"tp70b_decode": measure_tp70b(rank, world, args.steps, args.warmup, barrier, args.all_gather_forms)}
             if world > 1:
                 dist.barrier()
                 dist.destroy_process_group()

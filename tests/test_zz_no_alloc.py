@@ -6,7 +6,7 @@ with a fixed arena, a plug-in that does not own the allocator -- so
 the library.  This test calls it directly through the C ABI, twice in a row on
 different inputs (the second call must not see the first call's scratch), and
 requires every output stream to equal, bit for bit, what ``atlas_quantize``
-writes for the same input.
+writes for the same input and, once, what the CPU oracle computes.
 """
 import ctypes
 
@@ -14,6 +14,7 @@ import pytest
 import torch
 
 from atlasinfer_b200 import _capi
+from oracle import atlas_oracle as O
 from tests.util import bits, config_weights
 
 pytestmark = pytest.mark.gpu
@@ -63,8 +64,13 @@ def test_noalloc_matches_workspace_entry_point_twice(cuda_device):
     # and once more with the first input: stale scratch from a smaller call must not matter
     w, bs, thr = cases[0]
     wd = w.to(cuda_device).contiguous()
-    for a, b_ in zip(_run(wd, bs, thr, True), _run(wd, bs, thr, False)):
+    got = _run(wd, bs, thr, True)
+    for a, b_ in zip(got, _run(wd, bs, thr, False)):
         assert torch.equal(bits(a), bits(b_))
+    # the same streams as the CPU oracle, so the entry point is checked against the reference arithmetic itself
+    o = O.quantize(w, bs, thr)
+    for a, b_ in zip(got, (o.fp8_data, o.fp16_outliers, o.outlier_indices, o.scale_factors)):
+        assert a.shape == b_.shape and torch.equal(bits(a.cpu()), bits(b_))
 
 
 def test_noalloc_rejects_sizes_beyond_its_limit(cuda_device):
