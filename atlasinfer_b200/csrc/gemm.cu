@@ -48,12 +48,12 @@ namespace {
 
 constexpr int GM_DQ_WARPS = 16;                      // dequantizer warps: 4 TMEM lane quarters x 4 K-step phases
 constexpr int GM_EPI_WARPS = 16;                     // all of them drain the accumulator: four per TMEM lane quarter
-constexpr int GM_CTRL_WARPS = 3;                     // activation producer, MMA issuer, code producer
+constexpr int GM_CTRL_WARPS = 3;                     // activation producer (and converter), MMA issuer, code producer
 constexpr int GM_THREADS = (GM_CTRL_WARPS + GM_DQ_WARPS) * 32;
 constexpr int GM_BM = 128;  // weight rows (output features) per CTA = UMMA M
 constexpr int GM_BK = 64;   // K per pipeline step (one 128-byte swizzle row of fp16)
 constexpr int GM_SK = 2;    // k-tiles per pipeline stage: one barrier round trip, poll and commit per 128 columns of K
-constexpr int GM_XS = 2;    // activation ring depth, in stages
+// (the activation ring depth depends on the token tile too: Smem<BN>::XS)
 // (the code ring depth depends on the token tile: Smem<BN>::CS)
 constexpr int GM_PH = 4;    // K-stage phases of the dequantizers = `ready` / `mma_done` barriers
 constexpr int GM_A_COLS = GM_SK * GM_BK / 2;     // TMEM columns of one A stage: two fp16 per 32-bit cell
@@ -67,17 +67,20 @@ struct Smem {
     // tiles are HBM-bound and leave the room for a deep ring (160 KB in flight covers ~3 us of loaded DRAM latency
     // at an SM's share of the bandwidth); the 256-token tile is compute-bound and needs the room for activations.
     static constexpr int CS = BN <= 32 ? 10 : (BN == 64 ? 8 : (BN == 128 ? 6 : 4));
+    // Activation ring depth, in stages.  Decode-sized token tiles are filled by a warp (loads, conversion, stores:
+    // a microsecond of latency per stage), which a deeper ring hides; the wide tiles come in by TMA.
+    static constexpr int XS = BN <= 64 ? 4 : 2;
     static constexpr uint32_t OFF_B = 0;
-    static constexpr uint32_t OFF_C = OFF_B + GM_XS * GM_SK * B_BYTES;
+    static constexpr uint32_t OFF_C = OFF_B + XS * GM_SK * B_BYTES;
     static constexpr uint32_t OFF_BAR = OFF_C + CS * GM_SK * C_BYTES;
-    static constexpr uint32_t OFF_S = OFF_BAR + 256;
+    static constexpr uint32_t OFF_S = OFF_BAR + 512;
     static constexpr uint32_t TOTAL = OFF_S + CS * GM_SK * S_BYTES + 1024 /*alignment slack*/;
     // A stages in tensor memory (64 columns each) beside the accumulator columns [0, BN); allocations are powers of two
     static constexpr int A_STAGES = BN == 256 ? 4 : 2;
     static constexpr uint32_t TMEM_COLS = BN + A_STAGES * GM_A_COLS <= 256 ? 256 : 512;
     static_assert(BN + A_STAGES * GM_A_COLS <= 512, "tensor memory");
     // the epilogue stages the output tile over the (then idle) activation and code rings
-    static_assert((BN * (GM_BM + 4)) * 4 <= GM_XS * GM_SK * B_BYTES + CS * GM_SK * C_BYTES, "epilogue staging does not fit");
+    static_assert((BN * (GM_BM + 4)) * 4 <= XS * GM_SK * B_BYTES + CS * GM_SK * C_BYTES, "epilogue staging does not fit");
     static_assert(TOTAL <= 227 * 1024, "shared memory");
 };
 constexpr int GM_SPIN_LIMIT = 1 << 20;       // polls per wait
@@ -189,6 +192,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 template <int BN>
 constexpr uint32_t gm_idesc() { return (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24); }
 
+// Two bf16 (low, high half of v) -> two fp16, saturating at +-65504.
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(v & 0xffff0000u)), "f"(__uint_as_float(v << 16)));
+    return r;
+}
+
 // Four biased codes -> two half2 of fp16(fp16(code) * scale), as in the streaming kernel.
 __device__ __forceinline__ void dequant4(uint32_t w, __half2 scale2, uint32_t &lo, uint32_t &hi) {
     const uint32_t l = __byte_perm(w, 0x64646464u, 0x5140);
@@ -220,6 +230,11 @@ struct GemmParams {
     int splits;        // K slices (grid.z); > 1: fp32 partial tiles go to `partials`, a second kernel adds them
     float *partials;   // [splits][m][n_rows] fp32
     int to_partials;   // write the fp32 tile to `partials` even with one K slice (the second kernel writes y)
+    int x_bf16;        // the tensor map delivers bf16 rows (decode-sized token tiles only): converted in the kernel
+    const unsigned int *wait_flags;    // arrival flags of the ranks that fill x (gathered input), or null
+    const unsigned int *gather_state;  // [1]: this rank's count of completed gather launches
+    int wait_world;
+    long long poll_limit;
     int *error_flag;
 };
 
@@ -241,10 +256,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     auto ready_bar = [&](int s) { return bars + 8u * s; };
     auto mma_done = [&](int s) { return bars + 8u * (GM_PH + s); };
     auto full_c = [&](int s) { return bars + 8u * (2 * GM_PH + s); };
-    constexpr int CS = SM::CS;
+    constexpr int CS = SM::CS, XS = SM::XS;
     auto empty_c = [&](int s) { return bars + 8u * (2 * GM_PH + CS + s); };
-    constexpr int N_BARS = 2 * GM_PH + 2 * CS + 1;
-    static_assert(N_BARS * 8 + 16 <= 256, "barrier area");
+    auto x_landed = [&](int s) { return bars + 8u * (2 * GM_PH + 2 * CS + s); };   // bf16 tile in its slot, to be converted
+    constexpr int N_BARS = 2 * GM_PH + 2 * CS + XS + 1;
+    static_assert(N_BARS * 8 + 16 <= 512, "barrier area");
     const uint32_t accfull_bar = bars + 8u * (N_BARS - 1);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + OFF_BAR + 8 * N_BARS);
     volatile int *s_abort = reinterpret_cast<volatile int *>(base_ptr + OFF_BAR + 8 * N_BARS + 8);
@@ -257,7 +273,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
     const int kt_begin = (int)((long long)p.k_tiles * blockIdx.z / p.splits);
     const int KT = (int)((long long)p.k_tiles * (blockIdx.z + 1) / p.splits) - kt_begin;
     const int NST = (KT + GM_SK - 1) / GM_SK;   // pipeline stages of GM_SK k-tiles (the last one may hold a single k-tile)
-    // stage st uses barriers ready[st % 4] / mma_done[st % 4] in round st / 4, activation slot st % GM_XS, code slot
+    // stage st uses barriers ready[st % 4] / mma_done[st % 4] in round st / 4, activation slot st % XS, code slot
     // st % CS and A stage st % AS; a resource used by stage st is free again when mma_done of stage st fired
     auto done_bar_of = [&](int st) { return mma_done(st % GM_PH); };
     auto done_par_of = [&](int st) { return (uint32_t)((st / GM_PH) & 1); };
@@ -270,6 +286,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             mbar_init(ready_bar(s), 4 * 32 + 1);
             mbar_init(mma_done(s), 1);
         }
+        for (int s = 0; s < XS; ++s) mbar_init(x_landed(s), 1);
         for (int s = 0; s < CS; ++s) {
             mbar_init(full_c(s), 1);
             mbar_init(empty_c(s), 4);
@@ -290,18 +307,81 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
 
     if (warp == 0) {
         // ------------------------------ activation producer ------------------------------
-        if (lane == 0) {
-            // activations come from earlier kernels of the stream; everything else so far read only weights
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (int st = 0; st < NST; ++st) {
-                const int slot = st % GM_XS;
-                if (st >= GM_XS && !mbar_wait<32>(done_bar_of(st - GM_XS), done_par_of(st - GM_XS))) { *s_abort = 1; break; }
-                if (*s_abort) break;
+        // activations come from earlier kernels of the stream; everything else so far read only weights
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        bool alive = true;
+        if (p.wait_flags) {
+            // x is a gathered buffer that the other ranks fill: wait (bounded) until every rank has completed as many
+            // gather launches as this one; the code ring keeps filling meanwhile
+            const unsigned int target = *reinterpret_cast<const volatile unsigned int *>(p.gather_state + 1);
+            bool ok = true;
+            if (lane < p.wait_world) {
+                ok = false;
+                for (long long i = 0; i < p.poll_limit; ++i) {
+                    unsigned int v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + lane) : "memory");
+                    if ((int)(v - target) >= 0) { ok = true; break; }
+                    __nanosleep(64);
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok)) { alive = false; *s_abort = 1; }
+        }
+        // requests the activation tiles of stage `st` (lane 0); false if the slot never became free
+        auto request = [&](int st) -> bool {
+            const int slot = st % XS;
+            if (st >= XS && !mbar_wait<32>(done_bar_of(st - XS), done_par_of(st - XS))) return false;
+            const int nk = min(GM_SK, KT - st * GM_SK);
+            // bf16 tiles land in their slot and are converted there by this warp, which then reports the stage ready
+            const uint32_t rb = p.x_bf16 ? x_landed(slot) : ready_bar(st % GM_PH);
+            mbar_arrive_expect_tx(rb, (uint32_t)nk * B_BYTES);
+            for (int j = 0; j < nk; ++j)
+                tma_load_2d(base + OFF_B + (slot * GM_SK + j) * B_BYTES, &x_map, (kt_begin + st * GM_SK + j) * GM_BK, m0, rb);
+            return true;
+        };
+        if (BN <= 64 && p.x_bf16) {
+            // bf16 input, decode-sized token tiles.  The tensor map delivers the bf16 rows with the same 128-byte
+            // swizzle the MMA expects of the fp16 tile, so the conversion is element-wise in place: lane = token row,
+            // eight 16-byte pieces per row and k-tile.  The ring is kept XS - 1 stages ahead: the slot of stage st - 1
+            // is requested again after stage st has been converted, when its MMAs have normally finished.
+            bool ok = alive;
+            int requested = 0;
+            if (lane == 0 && ok)
+                for (; requested < NST && requested < XS - 1; ++requested) ok = request(requested);
+            requested = __shfl_sync(0xffffffffu, requested, 0);
+            for (int st = 0; st < NST && __all_sync(0xffffffffu, ok); ++st) {
+                const int slot = st % XS;
+                if (!mbar_wait_warp<32>(x_landed(slot), (uint32_t)((st / XS) & 1), s_abort)) { ok = false; break; }
                 const int nk = min(GM_SK, KT - st * GM_SK);
-                const uint32_t rb = ready_bar(st % GM_PH);
-                mbar_arrive_expect_tx(rb, (uint32_t)nk * B_BYTES);
-                for (int j = 0; j < nk; ++j)
-                    tma_load_2d(base + OFF_B + (slot * GM_SK + j) * B_BYTES, &x_map, (kt_begin + st * GM_SK + j) * GM_BK, m0, rb);
+                for (int j = 0; j < nk; ++j) {
+#pragma unroll
+                    for (int rr = 0; rr < BN / 32; ++rr) {
+                        unsigned char *row = base_ptr + OFF_B + (slot * GM_SK + j) * B_BYTES + (rr * 32 + lane) * 128;
+                        uint4 v[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4 *>(row + ((c ^ (lane & 7)) << 4));
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            v[c].x = bf16x2_to_f16x2(v[c].x);
+                            v[c].y = bf16x2_to_f16x2(v[c].y);
+                            v[c].z = bf16x2_to_f16x2(v[c].z);
+                            v[c].w = bf16x2_to_f16x2(v[c].w);
+                            *reinterpret_cast<uint4 *>(row + ((c ^ (lane & 7)) << 4)) = v[c];
+                        }
+                    }
+                }
+                fence_async_smem();   // the tensor core reads the tile through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(ready_bar(st % GM_PH));
+                    if (requested < NST) { ok = request(requested); }
+                }
+                if (requested < NST) ++requested;
+            }
+            if (!__all_sync(0xffffffffu, ok)) *s_abort = 1;
+        } else if (lane == 0 && alive) {
+            for (int st = 0; st < NST; ++st) {
+                if (*s_abort) break;
+                if (!request(st)) { *s_abort = 1; break; }
             }
         }
     } else if (warp == 2) {
@@ -338,7 +418,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ C
             const uint32_t ta0 = tmem_base + (uint32_t)BN;
             for (int st = 0; st < NST && ok; ++st) {
                 tcgen05_fence_after();
-                const uint64_t dbs = db0 + (uint64_t)(((st % GM_XS) * GM_SK * B_BYTES) >> 4);   // the address field counts 16-byte units
+                const uint64_t dbs = db0 + (uint64_t)(((st % XS) * GM_SK * B_BYTES) >> 4);   // the address field counts 16-byte units
                 const uint32_t ta = ta0 + (uint32_t)((st % AS) * GM_A_COLS);
                 const bool two = KT - st * GM_SK >= 2;
                 umma_f16_ts(tmem_base, ta, dbs, gm_idesc<BN>(), st != 0);
@@ -685,43 +765,16 @@ gemm_finish_kernel(const float *partials, int splits, int m, int n_rows, const u
     }
 }
 
-// bf16 -> fp16 (saturating) into a dense [m][k] buffer; also used to make strided fp16 rows dense.  When x is a
-// gathered buffer that the other ranks fill (`wait_flags`), every CTA first waits, bounded, until all ranks'
-// arrival counts have reached this rank's own (state[1]).
+// bf16 -> fp16 (saturating) into a dense [m][k] buffer; also used to make strided fp16 rows dense.
 __global__ void __launch_bounds__(256)
-to_f16_kernel(const uint16_t *x, int64_t ldx, int m, int k, int from_bf16, uint16_t *out, const unsigned int *wait_flags,
-              int wait_world, const unsigned int *state, long long poll_limit, int *status) {
+to_f16_kernel(const uint16_t *x, int64_t ldx, int m, int k, int from_bf16, uint16_t *out) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (wait_flags) {
-        if (threadIdx.x < 32) {
-            const int lane = threadIdx.x;
-            const unsigned int target = *reinterpret_cast<const volatile unsigned int *>(state + 1);
-            bool ok = true;
-            if (lane < wait_world) {
-                ok = false;
-                for (long long i = 0; i < poll_limit; ++i) {
-                    unsigned int v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait_flags + lane) : "memory");
-                    if ((int)(v - target) >= 0) { ok = true; break; }
-                    __nanosleep(64);
-                }
-            }
-            if (!__all_sync(0xffffffffu, ok) && lane == 0 && status) atomicExch(status, 1);   // reported; the copy goes on
-        }
-        __syncthreads();
-    }
     const int64_t total = (int64_t)m * (k >> 1);
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
         const int64_t row = i / (k >> 1), c2 = i - row * (k >> 1);
-        // (read through L2: with wait_flags the rows were written by other GPUs)
-        uint32_t v = __ldcg(x + row * ldx + 2 * c2) | (uint32_t)__ldcg(x + row * ldx + 2 * c2 + 1) << 16;
-        if (from_bf16) {
-            float lo = fminf(fmaxf(__uint_as_float(v << 16), -65504.f), 65504.f);
-            float hi = fminf(fmaxf(__uint_as_float(v & 0xffff0000u), -65504.f), 65504.f);
-            __half2 h = __floats2half2_rn(lo, hi);
-            v = *reinterpret_cast<uint32_t *>(&h);
-        }
+        uint32_t v = x[row * ldx + 2 * c2] | (uint32_t)x[row * ldx + 2 * c2 + 1] << 16;
+        if (from_bf16) v = bf16x2_to_f16x2(v);
         reinterpret_cast<uint32_t *>(out)[i] = v;
     }
 }
@@ -885,17 +938,25 @@ int gemm_entry(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *
     const void *xb = x;
     int64_t ldb = ldx;
     const size_t xcopy = ((size_t)m * (size_t)n_cols * 2 + 255) & ~(size_t)255;
-    const unsigned int *wait_flags = gather ? gather->wait_flags : nullptr;   // the wait lives in the copy kernel
-    const bool direct = dtype == ATLAS_DTYPE_F16 && ((uintptr_t)x & 15) == 0 && (ldx % 8) == 0 && !wait_flags;
+    const unsigned int *wait_flags = gather ? gather->wait_flags : nullptr;
+    // Rows the tensor map can take as they are: 16-byte aligned, fp16 -- or bf16 for decode-sized token tiles,
+    // which the kernel converts in shared memory.  Anything else is copied to a dense fp16 buffer first.
+    const bool tma_ok = ((uintptr_t)x & 15) == 0 && (ldx % 8) == 0;
+    // (in the kernel when the weight is small -- one more kernel in the chain then costs more than the converter warp's
+    // share of the issue slots over the few stages of a CTA -- and always for a gathered input, whose wait lives in
+    // the kernel)
+    const bool small_weight = n_rows * n_cols <= ((int64_t)32 << 20);
+    const bool in_kernel_bf16 = dtype == ATLAS_DTYPE_BF16 && bn <= 64 && tma_ok && (small_weight || wait_flags != nullptr);
+    const bool direct = tma_ok && (dtype == ATLAS_DTYPE_F16 || in_kernel_bf16);
+    ATLAS_RETURN_IF(wait_flags && !direct, ATLAS_ERR_UNSUPPORTED,
+                    "atlas_qlinear_gemm_gather: a gathered input must be 16-byte aligned with a row stride that is a multiple of 8");
     if (!direct) {
         uint16_t *xf = (uint16_t *)((char *)workspace + GM_WS_HEADER);
         const int64_t pairs = m * (n_cols / 2);
         const int64_t blocks = ceil_div_i64(pairs, 256);
         cudaLaunchConfig_t cfg = pdl_config(dim3((unsigned)(blocks < 65535 ? blocks : 65535)), dim3(256), 0, st);
         rc = check_cuda(cudaLaunchKernelEx(&cfg, to_f16_kernel, (const uint16_t *)x, ldx, (int)m, (int)n_cols,
-                                           (int)(dtype == ATLAS_DTYPE_BF16), xf, wait_flags, gather ? (int)gather->world : 0,
-                                           gather ? (const unsigned int *)gather->state : (const unsigned int *)nullptr,
-                                           gather ? (long long)gather->poll_limit : 0ll, (int *)status), "to_f16_kernel launch");
+                                           (int)(dtype == ATLAS_DTYPE_BF16), xf), "to_f16_kernel launch");
         if (rc) return rc;
         xb = xf;
         ldb = n_cols;
@@ -945,6 +1006,11 @@ int gemm_entry(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *
     p.splits = gemm_splits_for(m, n_rows, n_cols, gemm_sm_count());
     p.partials = (float *)((char *)workspace + GM_WS_HEADER + xcopy);
     p.to_partials = gather != nullptr;   // the gather is the second kernel's job
+    p.x_bf16 = in_kernel_bf16;
+    p.wait_flags = wait_flags;
+    p.gather_state = gather ? (const unsigned int *)gather->state : nullptr;
+    p.wait_world = gather ? gather->world : 0;
+    p.poll_limit = gather ? (long long)gather->poll_limit : 0;
     p.error_flag = status;
     switch (bn) {
         case 32: rc = launch_gemm<32>(x_map, c_map, p, st); break;

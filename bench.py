@@ -388,7 +388,7 @@ def measure_opt13b():
     return res
 
 
-def measure_tp70b(rank, world, steps, warmup, barrier, all_forms=False):
+def measure_tp70b(rank, world, steps, warmup, barrier, all_forms=False, shard_of=None):
     """Config 5: Llama-3-70B-shaped decode, batch 32, column-parallel over `world` ranks.
 
     Every rank owns rows [r*N/g, (r+1)*N/g) of each linear (8 distinct layers, cycled ten times to stand for the
@@ -402,7 +402,9 @@ def measure_tp70b(rank, world, steps, warmup, barrier, all_forms=False):
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev).manual_seed(777 + rank)
     layers, reps, m = 8, 10, 32
-    model = build_model(LLAMA70B_LINEARS, layers, gen, 0.015, fuse=True, rows_slice=(rank, world))
+    # shard_of: time one rank's share of a `shard_of`-way split on this GPU alone (no gather partners)
+    model = build_model(LLAMA70B_LINEARS, layers, gen, 0.015, fuse=True,
+                        rows_slice=(rank, world) if shard_of is None else (0, shard_of))
     xs = {k: torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16) for k in (8192, 28672)}
     # what a layer launches: (kernel layout of the launch, output rows it produces on this rank)
     from atlasinfer_b200.integration import atlas_wrappers as aw
@@ -744,6 +746,8 @@ def main():
     ap.add_argument("--all-gather-forms", action="store_true",
                     help="70B-shaped decode: also time the gather fused into the streaming kernel and the push kernel "
                          "(default: NCCL all-gather and the peer stores of the tcgen05 path)")
+    ap.add_argument("--shard-of", type=int, default=None,
+                    help="with --only tp70b on one GPU: time one rank's share of an N-way row split (no gathers)")
     ap.add_argument("--no-graph", action="store_true", help="launch the pass directly instead of replaying a graph")
     ap.add_argument("--only", default=None, choices=["gemm", "quantize", "opt13b", "tp70b"],
                     help="run just one of the secondary measurements and print it (for profiler captures)")
@@ -769,7 +773,8 @@ def main():
                 import torch.distributed as dist
                 dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=PG_TIMEOUT)
                 barrier = dist.barrier
-            out = {"tp70b_decode": measure_tp70b(rank, world, args.steps, args.warmup, barrier, args.all_gather_forms)}
+            out = {"tp70b_decode": measure_tp70b(rank, world, args.steps, args.warmup, barrier, args.all_gather_forms,
+                                                 args.shard_of)}
             if world > 1:
                 dist.barrier()
                 dist.destroy_process_group()
