@@ -748,10 +748,10 @@ gemm_finish_kernel(const float *partials, int splits, int m, int n_rows, const u
         // the CTA that finishes last tells every rank that this rank's columns are complete
         __syncthreads();
         if (threadIdx.x == 0) {
-            __threadfence_system();   // the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
+            asm volatile("fence.acq_rel.sys;" ::: "memory");   // releases the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
             const unsigned int finished = atomicAdd(fg.state, 1u);
             if (finished == gridDim.x - 1) {
-                __threadfence_system();
+                asm volatile("fence.acq_rel.sys;" ::: "memory");   // acquires the other CTAs' releases before the flags go out
                 const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(fg.state + 1) + 1u;
                 fg.state[0] = 0;
                 fg.state[1] = seq;

@@ -72,10 +72,10 @@ __global__ void __launch_bounds__(256) peer_push_kernel(PushParams p) {
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();   // the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
+        asm volatile("fence.acq_rel.sys;" ::: "memory");   // releases the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
         const unsigned int finished = atomicAdd(p.state, 1u);
         if (finished == gridDim.x - 1) {
-            __threadfence_system();
+            asm volatile("fence.acq_rel.sys;" ::: "memory");   // acquires the other CTAs' releases before the flags go out
             const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(p.state + 1) + 1u;
             p.state[0] = 0;
             p.state[1] = seq;

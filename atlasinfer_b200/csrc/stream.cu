@@ -729,10 +729,10 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
     __syncthreads();
     if (p.world > 1 && tid == 0) {
         // the CTA that finishes last tells every rank that this rank's shard of the output is complete
-        __threadfence_system();   // the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
+        asm volatile("fence.acq_rel.sys;" ::: "memory");   // releases the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
         const unsigned int finished = atomicAdd(p.state, 1u);
         if (finished == (unsigned int)grid - 1) {
-            __threadfence_system();
+            asm volatile("fence.acq_rel.sys;" ::: "memory");   // acquires the other CTAs' releases before the flags go out
             const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(p.state + 1) + 1u;
             p.state[0] = 0;
             p.state[1] = seq;
