@@ -30,7 +30,7 @@ namespace {
 struct GemvParams {
     const void *x;
     int dtype;
-    int m;          // rows of x handled by this launch (<= 8)
+    int m;          // rows of x handled by this launch (<= 16)
     int64_t ldx;
     const uint8_t *tiles;
     const uint16_t *scales_t;   // [row/128][block][row%128]
@@ -101,9 +101,13 @@ __device__ __forceinline__ void load_x16(const uint16_t *src, uint32_t (&xv)[8])
     }
 }
 
-template <bool BF16, bool VEC>
-__global__ void __launch_bounds__(GS_MAX_WARPS * 32, 2) gemv_strip_kernel(GemvParams p) {
-    __shared__ float4 part[GS_MAX_WARPS][32];
+// MT: 8-column MMA tiles over the batch (m <= 8 * MT).  One tile: two CTAs per SM at 64 registers, two k-tiles of
+// codes in flight per warp.  Two tiles: one CTA per SM at twice the registers, four k-tiles in flight per warp (the
+// same bytes in flight per SM), the dequantised fragments of a step feeding two MMAs.
+template <bool BF16, bool VEC, int MT>
+__global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip_kernel(GemvParams p) {
+    constexpr int U = MT == 1 ? GS_UNROLL : 2 * GS_UNROLL;
+    __shared__ float4 part[MT][GS_MAX_WARPS][32];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -115,15 +119,19 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, 2) gemv_strip_kernel(GemvPa
     const uint8_t *wbase = p.tiles + ((size_t)(strip >> 3) * p.k_tiles * 8 + (strip & 7)) * 1024 + lane * 16;
     const uint16_t *sbase = p.scales_t + (size_t)(strip >> 3) * p.blocks_per_row * 128 + (strip & 7) * 16 + g;
     // lanes whose batch row does not exist read row 0: their MMA columns are never stored
-    const uint16_t *xg = reinterpret_cast<const uint16_t *>(p.x) + (size_t)(g < p.m ? g : 0) * p.ldx;
-    const uint16_t *xrow = xg + tig * 16;
+    const uint16_t *xg[MT], *xrow[MT];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+        xg[nt] = reinterpret_cast<const uint16_t *>(p.x) + (size_t)(nt * 8 + g < p.m ? nt * 8 + g : 0) * p.ldx;
+        xrow[nt] = xg[nt] + tig * 16;
+    }
 
     // ---- weights first: none of this depends on earlier kernels of the stream ----------------------
-    uint4 wa[GS_UNROLL], wb[GS_UNROLL];
-    uint16_t sa[GS_UNROLL], sb[GS_UNROLL];
+    uint4 wa[U], wb[U];
+    uint16_t sa[U], sb[U];
     auto load_batch = [&](int kt) {
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
+        for (int u = 0; u < U; ++u) {
             if (kt + u < kt1) {
                 const uint8_t *tp = wbase + (size_t)(kt + u) * 8192;
                 wa[u] = ldg_stream(tp);
@@ -147,55 +155,85 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, 2) gemv_strip_kernel(GemvPa
         pre_val[q] = 0;
         if (e < e_end) { pre_ent[q] = __ldg(p.entries + e); pre_val[q] = __ldg(p.ovals + e); }
     }
-    const int rL = tid >> 2, rj = tid & 3;              // (lane, component) this thread reduces at the end
-    const int out_row = (rL >> 2) + (rj >> 1) * 8, out_m = (rL & 3) * 2 + (rj & 1);
+    // (MMA tile, lane, component) this thread reduces at the end: 128 outputs per tile
+    const int rT = tid >> 7, rL = (tid >> 2) & 31, rj = tid & 3;
+    const int out_row = (rL >> 2) + (rj >> 1) * 8, out_m = rT * 8 + (rL & 3) * 2 + (rj & 1);
     const int out_n = strip * 16 + out_row;
     float bias_v = 0.f;
-    if (tid < 128 && p.bias && out_n < p.n_rows) bias_v = __half2float(__ushort_as_half(__ldg(p.bias + out_n)));
+    if (tid < 128 * MT && p.bias && out_n < p.n_rows) bias_v = __half2float(__ushort_as_half(__ldg(p.bias + out_n)));
 
     // ---- activations: only after the earlier kernels of the stream have completed ------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[MT][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
     auto outlier_mma = [&](const uint32_t (&ent)[4], const uint32_t (&val)[4]) {
         int rws[4];
-        uint32_t xq[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            rws[q] = (int)(ent[q] >> 24);
-            xq[q] = __ldg(xg + (ent[q] & 0xffffffu));
-        }
+        for (int q = 0; q < 4; ++q) rws[q] = (int)(ent[q] >> 24);
         const uint32_t a0 = (rws[0] == g ? val[0] : 0u) | (rws[1] == g ? val[1] : 0u) << 16;
         const uint32_t a1 = (rws[0] == g + 8 ? val[0] : 0u) | (rws[1] == g + 8 ? val[1] : 0u) << 16;
         const uint32_t a2 = (rws[2] == g ? val[2] : 0u) | (rws[3] == g ? val[3] : 0u) << 16;
         const uint32_t a3 = (rws[2] == g + 8 ? val[2] : 0u) | (rws[3] == g + 8 ? val[3] : 0u) << 16;
-        uint32_t b0 = xq[0] | xq[1] << 16, b1 = xq[2] | xq[3] << 16;
-        if (BF16) {
-            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b0) : "f"(__uint_as_float(xq[1] << 16)), "f"(__uint_as_float(xq[0] << 16)));
-            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b1) : "f"(__uint_as_float(xq[3] << 16)), "f"(__uint_as_float(xq[2] << 16)));
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) {
+            uint32_t xq[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) xq[q] = __ldg(xg[nt] + (ent[q] & 0xffffffu));
+            uint32_t b0 = xq[0] | xq[1] << 16, b1 = xq[2] | xq[3] << 16;
+            if (BF16) {
+                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b0) : "f"(__uint_as_float(xq[1] << 16)), "f"(__uint_as_float(xq[0] << 16)));
+                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b1) : "f"(__uint_as_float(xq[3] << 16)), "f"(__uint_as_float(xq[2] << 16)));
+            }
+            mma_f16(acc[nt], a0, a1, a2, a3, b0, b1);
         }
-        mma_f16(acc, a0, a1, a2, a3, b0, b1);
     };
     if (e_begin < e_end) outlier_mma(pre_ent, pre_val);   // its activation gathers overlap the K loop's loads
 
-    for (int kt = kt0; kt < kt1; kt += GS_UNROLL) {
+    for (int kt = kt0; kt < kt1; kt += U) {
         if (kt != kt0) load_batch(kt);
-        uint32_t xv[GS_UNROLL][8];
+        if (MT == 1) {
+            // all activations of the batch first, then the arithmetic
+            uint32_t xv[U][8];
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u)
-            if (kt + u < kt1) load_x16<BF16, VEC>(xrow + (kt + u) * 64, xv[u]);
+            for (int u = 0; u < U; ++u)
+                if (kt + u < kt1) load_x16<BF16, VEC>(xrow[0] + (kt + u) * 64, xv[u]);
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
-            if (kt + u < kt1) {
-                const __half2 sa2 = __half2half2(__ushort_as_half(sa[u])), sb2 = __half2half2(__ushort_as_half(sb[u]));
-                const uint32_t wav[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w};
-                const uint32_t wbv[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
+            for (int u = 0; u < U; ++u) {
+                if (kt + u < kt1) {
+                    const __half2 sa2 = __half2half2(__ushort_as_half(sa[u])), sb2 = __half2half2(__ushort_as_half(sb[u]));
+                    const uint32_t wav[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w};
+                    const uint32_t wbv[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t alo, ahi, blo, bhi;
-                    dequant4(wav[i], sa2, alo, ahi);
-                    dequant4(wbv[i], sb2, blo, bhi);
-                    mma_f16(acc, alo, blo, ahi, bhi, xv[u][2 * i], xv[u][2 * i + 1]);
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t alo, ahi, blo, bhi;
+                        dequant4(wav[i], sa2, alo, ahi);
+                        dequant4(wbv[i], sb2, blo, bhi);
+                        mma_f16(acc[0], alo, blo, ahi, bhi, xv[u][2 * i], xv[u][2 * i + 1]);
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (kt + u < kt1) {
+                    uint32_t xv[MT][8];
+#pragma unroll
+                    for (int nt = 0; nt < MT; ++nt) load_x16<BF16, VEC>(xrow[nt] + (kt + u) * 64, xv[nt]);
+                    const __half2 sa2 = __half2half2(__ushort_as_half(sa[u])), sb2 = __half2half2(__ushort_as_half(sb[u]));
+                    const uint32_t wav[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w};
+                    const uint32_t wbv[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t alo, ahi, blo, bhi;
+                        dequant4(wav[i], sa2, alo, ahi);
+                        dequant4(wbv[i], sb2, blo, bhi);
+#pragma unroll
+                        for (int nt = 0; nt < MT; ++nt) mma_f16(acc[nt], alo, blo, ahi, bhi, xv[nt][2 * i], xv[nt][2 * i + 1]);
+                    }
                 }
             }
         }
@@ -212,11 +250,12 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, 2) gemv_strip_kernel(GemvPa
         outlier_mma(ent, val);
     }
 
-    part[warp][lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) part[nt][warp][lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
     __syncthreads();
-    if (tid < 128) {
+    if (tid < 128 * MT) {
         float s = bias_v;
-        for (int w = 0; w < nwarps; ++w) s += reinterpret_cast<const float *>(&part[w][rL])[rj];
+        for (int w = 0; w < nwarps; ++w) s += reinterpret_cast<const float *>(&part[rT][w][rL])[rj];
         if (out_m < p.m && out_n < p.n_rows) {
             if (BF16) reinterpret_cast<__nv_bfloat16 *>(p.y)[(size_t)out_m * p.ldy + out_n] = __float2bfloat16_rn(s);
             else reinterpret_cast<__half *>(p.y)[(size_t)out_m * p.ldy + out_n] = __float2half_rn(s);
@@ -224,9 +263,10 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, 2) gemv_strip_kernel(GemvPa
     }
 }
 
+template <int MT>
 int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
     int nwarps = p.n_chunks < GS_MAX_WARPS ? p.n_chunks : GS_MAX_WARPS;
-    if (nwarps < 4) nwarps = 4;  // the reduction needs 128 threads
+    if (nwarps < 4 * MT) nwarps = 4 * MT;  // the reduction needs 128 threads per MMA tile
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((p.n_rows + 15) / 16), 1, 1);
     cfg.blockDim = dim3((unsigned)(nwarps * 32), 1, 1);
@@ -237,8 +277,8 @@ int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    auto kern = p.dtype == ATLAS_DTYPE_BF16 ? (vec ? gemv_strip_kernel<true, true> : gemv_strip_kernel<true, false>)
-                                            : (vec ? gemv_strip_kernel<false, true> : gemv_strip_kernel<false, false>);
+    auto kern = p.dtype == ATLAS_DTYPE_BF16 ? (vec ? gemv_strip_kernel<true, true, MT> : gemv_strip_kernel<true, false, MT>)
+                                            : (vec ? gemv_strip_kernel<false, true, MT> : gemv_strip_kernel<false, false, MT>);
     return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "gemv_strip_kernel launch");
 }
 
@@ -288,11 +328,11 @@ extern "C" int atlas_qlinear_gemv(const void *x, int dtype, int64_t m, int64_t l
     p.bs_shift = (block_size & (block_size - 1)) == 0 ? __builtin_ctz((unsigned)block_size) : -1;
     const bool vec = (((uintptr_t)x & 15) == 0) && (ldx % 8 == 0);   // x rows allow 16-byte loads
     (void)status;   // no bounded wait in this kernel: nothing to report
-    for (int64_t m0 = 0; m0 < m; m0 += 8) {   // one launch per 8 rows: the later passes find most of the weight in L2
-        p.m = (int)(m - m0 < 8 ? m - m0 : 8);
+    for (int64_t m0 = 0; m0 < m; m0 += 16) {   // one launch per 16 rows: the later passes find most of the weight in L2
+        p.m = (int)(m - m0 < 16 ? m - m0 : 16);
         p.x = (const char *)x + (size_t)m0 * ldx * 2;
         p.y = (char *)y + (size_t)m0 * ldy * 2;
-        rc = launch_gemv_strip(p, vec, st);
+        rc = p.m <= 8 ? launch_gemv_strip<1>(p, vec, st) : launch_gemv_strip<2>(p, vec, st);
         if (rc) return rc;
     }
     return ATLAS_OK;
