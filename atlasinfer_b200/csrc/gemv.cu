@@ -19,7 +19,9 @@
 // outliers of its strip at a time into one more MMA: the A fragment holds each value in its own row and K slot,
 // the B fragment gathers the matching activations.
 //
-// More than 8 rows of x are served as one launch per 8 rows: the later passes find most of the weight in L2.
+// Up to 8 rows of x take one 8-column MMA tile (two CTAs per SM); 9..16 rows take two tiles per step in one pass
+// over the weight (one CTA per SM at twice the registers).  More rows are served 16 at a time: the later passes
+// find most of the weight in L2.
 #include <cuda_bf16.h>
 
 #include "common.cuh"

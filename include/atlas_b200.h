@@ -165,10 +165,10 @@ ATLAS_API int atlas_repack(const int8_t *codes, int64_t n_codes, const void *out
  * never clears it.
  *
  * atlas_qlinear_gemv: decode shapes, any m >= 1 (intended for m <= 16).  HBM-
- * bound: the rows of x are served 8 at a time by a kernel that gives each CTA
- * one 16-row strip of the weight, streams its codes with 16-byte loads,
- * dequantises in registers and adds the outlier products in the same launch
- * (the passes after the first find most of the weight in L2).  Activations
+ * bound: the rows of x are served up to 16 at a time by a kernel that gives
+ * each CTA one 16-row strip of the weight, streams its codes with 16-byte
+ * loads, dequantises in registers and adds the outlier products in the same
+ * launch (passes after the first find most of the weight in L2).  Activations
  * that are not 16-byte aligned are read two bytes at a time.  Launched with
  * programmatic dependent launch: only weights are read before the stream's
  * earlier work has completed.  The kernel has no bounded wait: `status` is
