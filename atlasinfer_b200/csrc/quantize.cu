@@ -456,16 +456,18 @@ __global__ void __launch_bounds__(QT_THREADS, (EPT <= 16 ? 5 : 2)) quantize_fast
                     std_h = f2h_bits(__double2float_rn(sqrt(m2 / (double)(BS - 1))));
                 }
                 const float den_f = h2f_bits(f2h_bits(__fadd_rn(h2f_bits(std_h), eps_f)));
-                const float rden = __frcp_rn(den_f);
+                // |d| / den against the threshold = |d| against threshold * den: the block's two bounds are one
+                // rounding away from exact, well inside the guard band they delimit
+                const float lo_b = fc.t_lo * den_f, hi_b = fc.t_hi * den_f;
                 // z test, outlier mask, absmax of the rest
                 unsigned int omask = 0;   // bit j: element j of this thread is an outlier
                 unsigned int maxabs = 0;  // fp32 bits of the largest |x| kept (bit patterns order like the values)
 #pragma unroll
                 for (int j = 0; j < EPT; ++j) {
                     const float d = h2f_bits(f2h_bits(__fsub_rn(f[j], mean_f)));
-                    const float a = fabsf(d) * rden;
-                    bool is_out = a > fc.t_hi;
-                    if (!is_out && a >= fc.t_lo) {   // inside the guard band: the exact rounded quotient decides
+                    const float a = fabsf(d);
+                    bool is_out = a > hi_b;
+                    if (!is_out && a >= lo_b) {   // inside the guard band: the exact rounded quotient decides
                         const float z = h2f_bits(f2h_bits(__fdiv_rn(d, den_f)));
                         is_out = fabsf(z) > fc.thr_f;
                     }
@@ -489,12 +491,14 @@ __global__ void __launch_bounds__(QT_THREADS, (EPT <= 16 ? 5 : 2)) quantize_fast
                 uint8_t *db = s_dense + b * DSTRIDE + l;
 #pragma unroll
                 for (int j = 0; j < EPT; ++j) {
-                    const float v = f[j] * rsc;
-                    uint16_t qh = f2h_bits(v * (1.f - 2.4e-7f));
-                    if (qh != f2h_bits(v * (1.f + 2.4e-7f))) qh = f2h_bits(__fdiv_rn(f[j], sc_f));  // near a rounding boundary
-                    float r = rintf(h2f_bits(qh));
-                    r = fminf(fmaxf(r, -127.0f), 127.0f);
-                    db[j * 8] = (uint8_t)(int)r;
+                    const float v = f[j] * rsc;   // within 2^-22 of x / scale
+                    uint16_t qh = f2h_bits(v);
+                    // fp16 keeps 10 of the 23 mantissa bits: v rounds the other way only if its 13 low bits are within a
+                    // few units of the midpoint 0x1000 (results below the fp16 normal range give code 0 either way)
+                    if (((__float_as_uint(v) & 0x1fffu) - (0x1000u - 8u)) <= 16u) qh = f2h_bits(__fdiv_rn(f[j], sc_f));
+                    int r = __half2int_rn(__ushort_as_half(qh));   // half to even, as torch.round
+                    r = max(-127, min(127, r));
+                    db[j * 8] = (uint8_t)r;
                 }
                 if (omask) {
 #pragma unroll
