@@ -765,15 +765,37 @@ gemm_finish_kernel(const float *partials, int splits, int m, int n_rows, const u
     }
 }
 
-// bf16 -> fp16 (saturating) into a dense [m][k] buffer; also used to make strided fp16 rows dense.
+// bf16 -> fp16 (saturating) into a dense [m][k] buffer; also used to make strided fp16 rows dense.  When x is a
+// gathered buffer that the other ranks fill (`wait_flags`), every CTA first waits, bounded, until all ranks'
+// arrival counts have reached this rank's own (state[1]).
 __global__ void __launch_bounds__(256)
-to_f16_kernel(const uint16_t *x, int64_t ldx, int m, int k, int from_bf16, uint16_t *out) {
+to_f16_kernel(const uint16_t *x, int64_t ldx, int m, int k, int from_bf16, uint16_t *out, const unsigned int *wait_flags,
+              int wait_world, const unsigned int *state, long long poll_limit, int *status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (wait_flags) {
+        if (threadIdx.x < 32) {
+            const int lane = threadIdx.x;
+            const unsigned int target = *reinterpret_cast<const volatile unsigned int *>(state + 1);
+            bool ok = true;
+            if (lane < wait_world) {
+                ok = false;
+                for (long long i = 0; i < poll_limit; ++i) {
+                    unsigned int v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait_flags + lane) : "memory");
+                    if ((int)(v - target) >= 0) { ok = true; break; }
+                    __nanosleep(64);
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok) && lane == 0 && status) atomicExch(status, 1);   // reported; the copy goes on
+        }
+        __syncthreads();
+    }
     const int64_t total = (int64_t)m * (k >> 1);
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
         const int64_t row = i / (k >> 1), c2 = i - row * (k >> 1);
-        uint32_t v = x[row * ldx + 2 * c2] | (uint32_t)x[row * ldx + 2 * c2 + 1] << 16;
+        // (read through L2: with wait_flags the rows were written by other GPUs)
+        uint32_t v = __ldcg(x + row * ldx + 2 * c2) | (uint32_t)__ldcg(x + row * ldx + 2 * c2 + 1) << 16;
         if (from_bf16) v = bf16x2_to_f16x2(v);
         reinterpret_cast<uint32_t *>(out)[i] = v;
     }
@@ -942,21 +964,23 @@ int gemm_entry(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *
     // Rows the tensor map can take as they are: 16-byte aligned, fp16 -- or bf16 for decode-sized token tiles,
     // which the kernel converts in shared memory.  Anything else is copied to a dense fp16 buffer first.
     const bool tma_ok = ((uintptr_t)x & 15) == 0 && (ldx % 8) == 0;
-    // (in the kernel when the weight is small -- one more kernel in the chain then costs more than the converter warp's
-    // share of the issue slots over the few stages of a CTA -- and always for a gathered input, whose wait lives in
-    // the kernel)
+    // (in the kernel when the weight is small: one more kernel in the chain then costs more than the conversion's
+    // share of the producer warp over the few stages of a CTA)
     const bool small_weight = n_rows * n_cols <= ((int64_t)32 << 20);
-    const bool in_kernel_bf16 = dtype == ATLAS_DTYPE_BF16 && bn <= 64 && tma_ok && (small_weight || wait_flags != nullptr);
+    const bool in_kernel_bf16 = dtype == ATLAS_DTYPE_BF16 && bn <= 64 && tma_ok && small_weight;
     const bool direct = tma_ok && (dtype == ATLAS_DTYPE_F16 || in_kernel_bf16);
-    ATLAS_RETURN_IF(wait_flags && !direct, ATLAS_ERR_UNSUPPORTED,
-                    "atlas_qlinear_gemm_gather: a gathered input must be 16-byte aligned with a row stride that is a multiple of 8");
+    // a gathered input is waited for by whichever kernel reads x first: the copy kernel, or the linear kernel itself
+    const bool wait_in_copy = wait_flags && !direct;
     if (!direct) {
         uint16_t *xf = (uint16_t *)((char *)workspace + GM_WS_HEADER);
         const int64_t pairs = m * (n_cols / 2);
         const int64_t blocks = ceil_div_i64(pairs, 256);
         cudaLaunchConfig_t cfg = pdl_config(dim3((unsigned)(blocks < 65535 ? blocks : 65535)), dim3(256), 0, st);
         rc = check_cuda(cudaLaunchKernelEx(&cfg, to_f16_kernel, (const uint16_t *)x, ldx, (int)m, (int)n_cols,
-                                           (int)(dtype == ATLAS_DTYPE_BF16), xf), "to_f16_kernel launch");
+                                           (int)(dtype == ATLAS_DTYPE_BF16), xf, wait_in_copy ? wait_flags : (const unsigned int *)nullptr,
+                                           gather ? (int)gather->world : 0,
+                                           gather ? (const unsigned int *)gather->state : (const unsigned int *)nullptr,
+                                           gather ? (long long)gather->poll_limit : 0ll, (int *)status), "to_f16_kernel launch");
         if (rc) return rc;
         xb = xf;
         ldb = n_cols;
@@ -1007,7 +1031,7 @@ int gemm_entry(const void *x, int dtype, int64_t m, int64_t ldx, const uint8_t *
     p.partials = (float *)((char *)workspace + GM_WS_HEADER + xcopy);
     p.to_partials = gather != nullptr;   // the gather is the second kernel's job
     p.x_bf16 = in_kernel_bf16;
-    p.wait_flags = wait_flags;
+    p.wait_flags = wait_in_copy ? nullptr : wait_flags;
     p.gather_state = gather ? (const unsigned int *)gather->state : nullptr;
     p.wait_world = gather ? gather->world : 0;
     p.poll_limit = gather ? (long long)gather->poll_limit : 0;
