@@ -746,19 +746,22 @@ gemm_finish_kernel(const float *partials, int splits, int m, int n_rows, const u
     }
     if (fg.world > 0) {
         // the CTA that finishes last tells every rank that this rank's columns are complete
+        // Each CTA counts itself in with a release at GPU scope (the barrier orders the CTA's stores before it); the
+        // last one acquires the others' releases by the same atomic and releases everything at system scope with
+        // the flag stores themselves.  No stand-alone system fence: two of them in a row cost ~8 us per launch.
         __syncthreads();
         if (threadIdx.x == 0) {
-            asm volatile("fence.acq_rel.sys;" ::: "memory");   // releases the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
-            const unsigned int finished = atomicAdd(fg.state, 1u);
+            unsigned int finished;
+            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(finished) : "l"(fg.state) : "memory");
             if (finished == gridDim.x - 1) {
-                asm volatile("fence.acq_rel.sys;" ::: "memory");   // acquires the other CTAs' releases before the flags go out
                 const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(fg.state + 1) + 1u;
                 fg.state[0] = 0;
                 fg.state[1] = seq;
+                asm volatile("fence.acq_rel.sys;" ::: "memory");   // one system-scope release for all the flag stores
                 for (int d = 0; d < fg.world; ++d) {
                     int to = fg.rank + d;
                     if (to >= fg.world) to -= fg.world;
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(fg.flags_dst[to] + fg.rank), "r"(seq) : "memory");
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(fg.flags_dst[to] + fg.rank), "r"(seq) : "memory");
                 }
             }
         }

@@ -70,19 +70,21 @@ __global__ void __launch_bounds__(256) peer_push_kernel(PushParams p) {
                 if (off[u] >= 0) *reinterpret_cast<T *>(p.dst[to] + off[u]) = v[u];
         }
     }
+    // each CTA counts itself in with a release at GPU scope (the barrier orders the CTA's stores before it); the last
+    // one acquires the others' releases by the same atomic and releases everything at system scope with the flag stores
     __syncthreads();
     if (threadIdx.x == 0) {
-        asm volatile("fence.acq_rel.sys;" ::: "memory");   // releases the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
-        const unsigned int finished = atomicAdd(p.state, 1u);
+        unsigned int finished;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(finished) : "l"(p.state) : "memory");
         if (finished == gridDim.x - 1) {
-            asm volatile("fence.acq_rel.sys;" ::: "memory");   // acquires the other CTAs' releases before the flags go out
             const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(p.state + 1) + 1u;
             p.state[0] = 0;
             p.state[1] = seq;
+            asm volatile("fence.acq_rel.sys;" ::: "memory");   // one system-scope release for all the flag stores
             for (int d = 0; d < p.world; ++d) {
                 int to = p.rank + d;
                 if (to >= p.world) to -= p.world;
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags_dst[to] + p.rank), "r"(seq) : "memory");
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.flags_dst[to] + p.rank), "r"(seq) : "memory");
             }
         }
     }

@@ -102,9 +102,6 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 // Wait until every rank's arrival flag has reached `target` (a launch count); one lane per rank polls, at most
 // `limit` times.  Returns false if the limit ran out.
 __device__ __forceinline__ bool wait_arrivals(const unsigned int *flags, int world, unsigned int target, long long limit,
@@ -728,15 +725,18 @@ __global__ void __launch_bounds__(StreamCfg<MT>::THREADS, 2) qlinear_stream_kern
 
     __syncthreads();
     if (p.world > 1 && tid == 0) {
-        // the CTA that finishes last tells every rank that this rank's shard of the output is complete
-        asm volatile("fence.acq_rel.sys;" ::: "memory");   // releases the CTA's stores into the other ranks' buffers (ordered before this by the barrier)
-        const unsigned int finished = atomicAdd(p.state, 1u);
+        // The CTA that finishes last tells every rank that this rank's shard of the output is complete.  Each CTA counts
+        // itself in with a release at GPU scope (the barrier orders its stores before it); the last one acquires the
+        // others' releases by the same atomic and releases everything at system scope with the flag stores.
+        unsigned int finished;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(finished) : "l"(p.state) : "memory");
         if (finished == (unsigned int)grid - 1) {
-            asm volatile("fence.acq_rel.sys;" ::: "memory");   // acquires the other CTAs' releases before the flags go out
             const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(p.state + 1) + 1u;
             p.state[0] = 0;
             p.state[1] = seq;
-            for (int d = 0; d < p.world; ++d) st_release_sys(p.flags_dst[(p.rank + d) % p.world] + p.rank, seq);
+            asm volatile("fence.acq_rel.sys;" ::: "memory");   // one system-scope release for all the flag stores
+            for (int d = 0; d < p.world; ++d)
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.flags_dst[(p.rank + d) % p.world] + p.rank), "r"(seq) : "memory");
         }
     }
     if (*s_abort) {
