@@ -106,10 +106,15 @@ __device__ __forceinline__ void load_x16(const uint16_t *src, uint32_t (&xv)[8])
 // MT: 8-column MMA tiles over the batch (m <= 8 * MT).  One tile: two CTAs per SM at 64 registers, two k-tiles of
 // codes in flight per warp.  Two tiles: one CTA per SM at twice the registers, four k-tiles in flight per warp (the
 // same bytes in flight per SM), the dequantised fragments of a step feeding two MMAs.
-template <bool BF16, bool VEC, int MT>
+//
+// STAGE (bf16 activations, a single row): the CTA converts the row to fp16 once, into shared memory, instead of every
+// warp converting the fragments of every step in registers -- the kernel is bound by instruction
+// issue (about 120 issue slots per KB of codes, a fifth of them that conversion), not by bytes in flight.
+template <bool BF16, bool VEC, int MT, bool STAGE>
 __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip_kernel(GemvParams p) {
     constexpr int U = MT == 1 ? GS_UNROLL : 2 * GS_UNROLL;
     __shared__ float4 part[MT][GS_MAX_WARPS][32];
+    extern __shared__ __align__(16) unsigned char xs_raw[];   // STAGE: [m][n_cols fp16 + 16 bytes of padding]
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -166,6 +171,25 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
 
     // ---- activations: only after the earlier kernels of the stream have completed ------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int xs_row_bytes = p.n_cols * 2 + 16;
+    if (STAGE) {
+        const int per_row = p.n_cols >> 3;   // 16-byte pieces per row
+        const int total = p.m * per_row;
+        for (int idx = tid; idx < total; idx += blockDim.x) {
+            const int row = idx / per_row, c = idx - row * per_row;
+            uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.x) + (size_t)row * p.ldx) + c);
+            uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(w4[e] << 16), hi = __uint_as_float(w4[e] & 0xffff0000u);
+                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w4[e]) : "f"(hi), "f"(lo));
+            }
+            *reinterpret_cast<uint4 *>(xs_raw + (size_t)row * xs_row_bytes + c * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        }
+        __syncthreads();
+    }
+    // this lane's row of staged activations (rows that do not exist read row 0, as above)
+    const unsigned char *xs_lane = xs_raw + (size_t)(g < p.m ? g : 0) * xs_row_bytes;
 
     float acc[MT][4];
 #pragma unroll
@@ -184,9 +208,11 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
         for (int nt = 0; nt < MT; ++nt) {
             uint32_t xq[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) xq[q] = __ldg(xg[nt] + (ent[q] & 0xffffffu));
+            for (int q = 0; q < 4; ++q)
+                xq[q] = STAGE ? *reinterpret_cast<const uint16_t *>(xs_lane + (size_t)(ent[q] & 0xffffffu) * 2)
+                              : __ldg(xg[nt] + (ent[q] & 0xffffffu));
             uint32_t b0 = xq[0] | xq[1] << 16, b1 = xq[2] | xq[3] << 16;
-            if (BF16) {
+            if (BF16 && !STAGE) {
                 asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b0) : "f"(__uint_as_float(xq[1] << 16)), "f"(__uint_as_float(xq[0] << 16)));
                 asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(b1) : "f"(__uint_as_float(xq[3] << 16)), "f"(__uint_as_float(xq[2] << 16)));
             }
@@ -202,13 +228,22 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
             uint32_t xv[U][8];
 #pragma unroll
             for (int u = 0; u < U; ++u)
-                if (kt + u < kt1) load_x16<BF16, VEC>(xrow[0] + (kt + u) * 64, xv[u]);
+                if (kt + u < kt1) {
+                    if (STAGE) {
+                        const uint4 a = *reinterpret_cast<const uint4 *>(xs_lane + ((kt + u) * 64 + tig * 16) * 2);
+                        const uint4 b = *reinterpret_cast<const uint4 *>(xs_lane + ((kt + u) * 64 + tig * 16) * 2 + 16);
+                        xv[u][0] = a.x; xv[u][1] = a.y; xv[u][2] = a.z; xv[u][3] = a.w;
+                        xv[u][4] = b.x; xv[u][5] = b.y; xv[u][6] = b.z; xv[u][7] = b.w;
+                    } else {
+                        load_x16<BF16, VEC>(xrow[0] + (kt + u) * 64, xv[u]);
+                    }
+                }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (kt + u < kt1) {
-                    const __half2 sa2 = __half2half2(__ushort_as_half(sa[u])), sb2 = __half2half2(__ushort_as_half(sb[u]));
                     const uint32_t wav[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w};
                     const uint32_t wbv[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
+                    const __half2 sa2 = __half2half2(__ushort_as_half(sa[u])), sb2 = __half2half2(__ushort_as_half(sb[u]));
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint32_t alo, ahi, blo, bhi;
@@ -265,22 +300,41 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
     }
 }
 
+constexpr int GS_STAGE_MAX_BYTES = 48 * 1024;   // staged fp16 activations per CTA, at most (two CTAs per SM)
+
 template <int MT>
 int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
     int nwarps = p.n_chunks < GS_MAX_WARPS ? p.n_chunks : GS_MAX_WARPS;
     if (nwarps < 4 * MT) nwarps = 4 * MT;  // the reduction needs 128 threads per MMA tile
+    // a single row of bf16 activations is converted once per CTA into shared memory (measured: +3 % at one row, nothing
+    // at two)
+    const size_t stage_bytes = (size_t)p.m * ((size_t)p.n_cols * 2 + 16);
+    const bool stage = MT == 1 && p.dtype == ATLAS_DTYPE_BF16 && vec && p.m == 1 && stage_bytes <= (size_t)GS_STAGE_MAX_BYTES;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((p.n_rows + 15) / 16), 1, 1);
     cfg.blockDim = dim3((unsigned)(nwarps * 32), 1, 1);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = stage ? stage_bytes : 0;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    auto kern = p.dtype == ATLAS_DTYPE_BF16 ? (vec ? gemv_strip_kernel<true, true, MT> : gemv_strip_kernel<true, false, MT>)
-                                            : (vec ? gemv_strip_kernel<false, true, MT> : gemv_strip_kernel<false, false, MT>);
+    if (stage) {
+        auto kern = gemv_strip_kernel<true, true, 1, true>;
+        static thread_local int configured_dev = -1;   // more than the default dynamic shared memory: opt in once per device
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (configured_dev != dev) {
+            int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GS_STAGE_MAX_BYTES),
+                                "cudaFuncSetAttribute(gemv smem)");
+            if (rc) return rc;
+            configured_dev = dev;
+        }
+        return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "gemv_strip_kernel launch");
+    }
+    auto kern = p.dtype == ATLAS_DTYPE_BF16 ? (vec ? gemv_strip_kernel<true, true, MT, false> : gemv_strip_kernel<true, false, MT, false>)
+                                            : (vec ? gemv_strip_kernel<false, true, MT, false> : gemv_strip_kernel<false, false, MT, false>);
     return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "gemv_strip_kernel launch");
 }
 
