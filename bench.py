@@ -22,7 +22,8 @@ offload_canonical), so a step is 4 launches per layer, 128 in all.
             NCCL all-gather and with the kernels' own peer stores, and the
             layer-sharded quantization; in the single-GPU run also the figures
             that do not depend on N: the same pass without fusing (224
-            launches), batch 4 / 16 / 32, prefill GEMM TFLOP/s, quantize GB/s,
+            launches), batch 4 / 16 / 32, batch 1 with fp16 activations (the
+            reference's dtype), prefill GEMM TFLOP/s, quantize GB/s,
             the OPT-1.3B-architecture model end to end (quantize seconds,
             greedy decode tokens/s)
 
@@ -663,6 +664,9 @@ def run_ours(args, rank, world, local_rank):
         for m in (4, 16, 32):
             b, s, _ = measure_gemv(model, m, half, 3)
             extra[f"decode_m{m}_gbs"] = b * half / s / 1e9
+        # the reference's own activation dtype (its F.linear takes fp16 only): no conversion inside the kernel
+        b, s, _ = measure_gemv(model, 1, half, 3, dtype=torch.float16)
+        extra["decode_m1_fp16_activations_gbs"] = b * half / s / 1e9
     del model
     torch.cuda.empty_cache()
     if single and not args.no_fuse:
