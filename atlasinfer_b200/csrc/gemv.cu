@@ -110,7 +110,10 @@ __device__ __forceinline__ void load_x16(const uint16_t *src, uint32_t (&xv)[8])
 // STAGE (bf16 activations, a single row): the CTA converts the row to fp16 once, into shared memory, instead of every
 // warp converting the fragments of every step in registers -- the kernel is bound by instruction
 // issue (about 120 issue slots per KB of codes, a fifth of them that conversion), not by bytes in flight.
-template <bool BF16, bool VEC, int MT, bool STAGE>
+//
+// FAST (whole 256-column chunks, blocks of whole 64-column tiles): every batch of a warp is full and a step has one
+// scale block, so the K loop carries no bounds predicates and no per-lane block index.
+template <bool BF16, bool VEC, int MT, bool STAGE, bool FAST>
 __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip_kernel(GemvParams p) {
     constexpr int U = MT == 1 ? GS_UNROLL : 2 * GS_UNROLL;
     __shared__ float4 part[MT][GS_MAX_WARPS][32];
@@ -120,7 +123,9 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int g = lane >> 2, tig = lane & 3;
     const int strip = blockIdx.x;
-    const int c0 = (p.n_chunks * warp) / nwarps, c1 = (p.n_chunks * (warp + 1)) / nwarps;
+    // (a CTA has 16 warps unless K is short: the split of the chunks over them then needs no division)
+    const int c0 = nwarps == 16 ? (p.n_chunks * warp) >> 4 : (p.n_chunks * warp) / nwarps;
+    const int c1 = nwarps == 16 ? (p.n_chunks * (warp + 1)) >> 4 : (p.n_chunks * (warp + 1)) / nwarps;
     const int kt0 = c0 * 4, kt1 = min(c1 * 4, p.k_tiles);
 
     const uint8_t *wbase = p.tiles + ((size_t)(strip >> 3) * p.k_tiles * 8 + (strip & 7)) * 1024 + lane * 16;
@@ -139,13 +144,14 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
     auto load_batch = [&](int kt) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            if (kt + u < kt1) {
-                const uint8_t *tp = wbase + (size_t)(kt + u) * 8192;
+            if (FAST || kt + u < kt1) {
+                const uint8_t *tp = wbase + (FAST ? (size_t)((uint32_t)(kt + u) << 13) : (size_t)(kt + u) * 8192);
                 wa[u] = ldg_stream(tp);
                 wb[u] = ldg_stream(tp + 512);
-                const int kb = p.bs_shift >= 0 ? ((kt + u) * 64 + tig * 16) >> p.bs_shift : ((kt + u) * 64 + tig * 16) / p.bs;
-                sa[u] = __ldg(sbase + (size_t)kb * 128);
-                sb[u] = __ldg(sbase + (size_t)kb * 128 + 8);
+                const int kb = FAST ? (kt + u) >> (p.bs_shift - 6)
+                                    : (p.bs_shift >= 0 ? ((kt + u) * 64 + tig * 16) >> p.bs_shift : ((kt + u) * 64 + tig * 16) / p.bs);
+                sa[u] = __ldg(sbase + (FAST ? (size_t)((uint32_t)kb << 7) : (size_t)kb * 128));
+                sb[u] = __ldg(sbase + (FAST ? (size_t)((uint32_t)kb << 7) : (size_t)kb * 128) + 8);
             }
         }
     };
@@ -176,7 +182,7 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
         const int per_row = p.n_cols >> 3;   // 16-byte pieces per row
         const int total = p.m * per_row;
         for (int idx = tid; idx < total; idx += blockDim.x) {
-            const int row = idx / per_row, c = idx - row * per_row;
+            const int row = p.m == 1 ? 0 : idx / per_row, c = idx - row * per_row;
             uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.x) + (size_t)row * p.ldx) + c);
             uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -228,7 +234,7 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
             uint32_t xv[U][8];
 #pragma unroll
             for (int u = 0; u < U; ++u)
-                if (kt + u < kt1) {
+                if (FAST || kt + u < kt1) {
                     if (STAGE) {
                         const uint4 a = *reinterpret_cast<const uint4 *>(xs_lane + ((kt + u) * 64 + tig * 16) * 2);
                         const uint4 b = *reinterpret_cast<const uint4 *>(xs_lane + ((kt + u) * 64 + tig * 16) * 2 + 16);
@@ -240,7 +246,7 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
                 }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                if (kt + u < kt1) {
+                if (FAST || kt + u < kt1) {
                     const uint32_t wav[4] = {wa[u].x, wa[u].y, wa[u].z, wa[u].w};
                     const uint32_t wbv[4] = {wb[u].x, wb[u].y, wb[u].z, wb[u].w};
                     const __half2 sa2 = __half2half2(__ushort_as_half(sa[u])), sb2 = __half2half2(__ushort_as_half(sb[u]));
@@ -309,6 +315,7 @@ int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
     // a single row of bf16 activations is converted once per CTA into shared memory (measured: +3 % at one row, nothing
     // at two)
     const size_t stage_bytes = (size_t)p.m * ((size_t)p.n_cols * 2 + 16);
+    const bool fast = MT == 1 && vec && (p.k_tiles & 3) == 0 && p.bs_shift >= 6;   // whole chunks, blocks of whole tiles
     const bool stage = MT == 1 && p.dtype == ATLAS_DTYPE_BF16 && vec && p.m == 1 && stage_bytes <= (size_t)GS_STAGE_MAX_BYTES;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((p.n_rows + 15) / 16), 1, 1);
@@ -321,20 +328,24 @@ int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (stage) {
-        auto kern = gemv_strip_kernel<true, true, 1, true>;
-        static thread_local int configured_dev = -1;   // more than the default dynamic shared memory: opt in once per device
+        auto kern = fast ? gemv_strip_kernel<true, true, 1, true, true> : gemv_strip_kernel<true, true, 1, true, false>;
+        static thread_local int configured_dev[2] = {-1, -1};   // more than the default dynamic shared memory: opt in once
         int dev = 0;
         cudaGetDevice(&dev);
-        if (configured_dev != dev) {
+        if (configured_dev[fast] != dev) {
             int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GS_STAGE_MAX_BYTES),
                                 "cudaFuncSetAttribute(gemv smem)");
             if (rc) return rc;
-            configured_dev = dev;
+            configured_dev[fast] = dev;
         }
         return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "gemv_strip_kernel launch");
     }
-    auto kern = p.dtype == ATLAS_DTYPE_BF16 ? (vec ? gemv_strip_kernel<true, true, MT, false> : gemv_strip_kernel<true, false, MT, false>)
-                                            : (vec ? gemv_strip_kernel<false, true, MT, false> : gemv_strip_kernel<false, false, MT, false>);
+    if (fast && MT == 1) {
+        auto kern = p.dtype == ATLAS_DTYPE_BF16 ? gemv_strip_kernel<true, true, 1, false, true> : gemv_strip_kernel<false, true, 1, false, true>;
+        return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "gemv_strip_kernel launch");
+    }
+    auto kern = p.dtype == ATLAS_DTYPE_BF16 ? (vec ? gemv_strip_kernel<true, true, MT, false, false> : gemv_strip_kernel<true, false, MT, false, false>)
+                                            : (vec ? gemv_strip_kernel<false, true, MT, false, false> : gemv_strip_kernel<false, false, MT, false, false>);
     return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "gemv_strip_kernel launch");
 }
 
