@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
         } else {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                if (kt + u < kt1) {
+                if (FAST || kt + u < kt1) {
                     uint32_t xv[MT][8];
 #pragma unroll
                     for (int nt = 0; nt < MT; ++nt) load_x16<BF16, VEC>(xrow[nt] + (kt + u) * 64, xv[nt]);
@@ -315,7 +315,7 @@ int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
     // a single row of bf16 activations is converted once per CTA into shared memory (measured: +3 % at one row, nothing
     // at two)
     const size_t stage_bytes = (size_t)p.m * ((size_t)p.n_cols * 2 + 16);
-    const bool fast = MT == 1 && vec && (p.k_tiles & 3) == 0 && p.bs_shift >= 6;   // whole chunks, blocks of whole tiles
+    const bool fast = vec && (p.k_tiles & 3) == 0 && p.bs_shift >= 6;   // whole chunks, blocks of whole tiles
     const bool stage = MT == 1 && p.dtype == ATLAS_DTYPE_BF16 && vec && p.m == 1 && stage_bytes <= (size_t)GS_STAGE_MAX_BYTES;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((p.n_rows + 15) / 16), 1, 1);
@@ -340,8 +340,8 @@ int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
         }
         return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "gemv_strip_kernel launch");
     }
-    if (fast && MT == 1) {
-        auto kern = p.dtype == ATLAS_DTYPE_BF16 ? gemv_strip_kernel<true, true, 1, false, true> : gemv_strip_kernel<false, true, 1, false, true>;
+    if (fast) {
+        auto kern = p.dtype == ATLAS_DTYPE_BF16 ? gemv_strip_kernel<true, true, MT, false, true> : gemv_strip_kernel<false, true, MT, false, true>;
         return check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "gemv_strip_kernel launch");
     }
     auto kern = p.dtype == ATLAS_DTYPE_BF16 ? (vec ? gemv_strip_kernel<true, true, MT, false, false> : gemv_strip_kernel<true, false, MT, false, false>)
