@@ -19,8 +19,8 @@
 // outliers of its strip at a time into one more MMA: the A fragment holds each value in its own row and K slot,
 // the B fragment gathers the matching activations.
 //
-// Up to 8 rows of x take one 8-column MMA tile (two CTAs per SM); 9..16 rows take two tiles per step in one pass
-// over the weight (one CTA per SM at twice the registers).  More rows are served 16 at a time: the later passes
+// Up to 8 rows of x take one 8-column MMA tile (two CTAs of 16 warps per SM); 9..16 rows take two tiles per step in
+// one pass over the weight (two CTAs of 8 warps per SM at twice the registers).  More rows are served 16 at a time: the later passes
 // find most of the weight in L2.
 #include <cuda_bf16.h>
 
@@ -74,6 +74,7 @@ __device__ __forceinline__ void dequant4(uint32_t w, __half2 scale2, uint32_t &l
 
 constexpr int GS_MAX_WARPS = 16;
 constexpr int GS_UNROLL = 2;
+constexpr int GS_WARPS2 = 8;   // warps of the two-tile kernel: two CTAs per SM at 128 registers (1.95 -> 2.38 TB/s at 16 rows against 16 warps in one CTA)
 
 __device__ __forceinline__ uint4 ldg_stream(const void *p) {
     uint4 v;
@@ -103,9 +104,9 @@ __device__ __forceinline__ void load_x16(const uint16_t *src, uint32_t (&xv)[8])
     }
 }
 
-// MT: 8-column MMA tiles over the batch (m <= 8 * MT).  One tile: two CTAs per SM at 64 registers, two k-tiles of
-// codes in flight per warp.  Two tiles: one CTA per SM at twice the registers, four k-tiles in flight per warp (the
-// same bytes in flight per SM), the dequantised fragments of a step feeding two MMAs.
+// MT: 8-column MMA tiles over the batch (m <= 8 * MT).  One tile: two CTAs of 16 warps per SM at 64 registers, two
+// k-tiles of codes in flight per warp.  Two tiles: two CTAs of 8 warps per SM at twice the registers, four k-tiles in
+// flight per warp (the same bytes in flight per SM), the dequantised fragments of a step feeding two MMAs.
 //
 // STAGE (bf16 activations, a single row): the CTA converts the row to fp16 once, into shared memory, instead of every
 // warp converting the fragments of every step in registers -- the kernel is bound by instruction
@@ -114,9 +115,9 @@ __device__ __forceinline__ void load_x16(const uint16_t *src, uint32_t (&xv)[8])
 // FAST (whole 256-column chunks, blocks of whole 64-column tiles): every batch of a warp is full and a step has one
 // scale block, so the K loop carries no bounds predicates and no per-lane block index.
 template <bool BF16, bool VEC, int MT, bool STAGE, bool FAST>
-__global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip_kernel(GemvParams p) {
+__global__ void __launch_bounds__((MT == 1 ? GS_MAX_WARPS : GS_WARPS2) * 32, 2) gemv_strip_kernel(GemvParams p) {
     constexpr int U = MT == 1 ? GS_UNROLL : 2 * GS_UNROLL;
-    __shared__ float4 part[MT][GS_MAX_WARPS][32];
+    __shared__ float4 part[MT][MT == 1 ? GS_MAX_WARPS : GS_WARPS2][32];
     extern __shared__ __align__(16) unsigned char xs_raw[];   // STAGE: [m][n_cols fp16 + 16 bytes of padding]
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -124,8 +125,8 @@ __global__ void __launch_bounds__(GS_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_strip
     const int g = lane >> 2, tig = lane & 3;
     const int strip = blockIdx.x;
     // (a CTA has 16 warps unless K is short: the split of the chunks over them then needs no division)
-    const int c0 = nwarps == 16 ? (p.n_chunks * warp) >> 4 : (p.n_chunks * warp) / nwarps;
-    const int c1 = nwarps == 16 ? (p.n_chunks * (warp + 1)) >> 4 : (p.n_chunks * (warp + 1)) / nwarps;
+    const int c0 = nwarps == 16 ? (p.n_chunks * warp) >> 4 : (nwarps == 8 ? (p.n_chunks * warp) >> 3 : (p.n_chunks * warp) / nwarps);
+    const int c1 = nwarps == 16 ? (p.n_chunks * (warp + 1)) >> 4 : (nwarps == 8 ? (p.n_chunks * (warp + 1)) >> 3 : (p.n_chunks * (warp + 1)) / nwarps);
     const int kt0 = c0 * 4, kt1 = min(c1 * 4, p.k_tiles);
 
     const uint8_t *wbase = p.tiles + ((size_t)(strip >> 3) * p.k_tiles * 8 + (strip & 7)) * 1024 + lane * 16;
@@ -310,7 +311,8 @@ constexpr int GS_STAGE_MAX_BYTES = 48 * 1024;   // staged fp16 activations per C
 
 template <int MT>
 int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
-    int nwarps = p.n_chunks < GS_MAX_WARPS ? p.n_chunks : GS_MAX_WARPS;
+    const int max_warps = MT == 1 ? GS_MAX_WARPS : GS_WARPS2;
+    int nwarps = p.n_chunks < max_warps ? p.n_chunks : max_warps;
     if (nwarps < 4 * MT) nwarps = 4 * MT;  // the reduction needs 128 threads per MMA tile
     // a single row of bf16 activations is converted once per CTA into shared memory (measured: +3 % at one row, nothing
     // at two)
