@@ -59,6 +59,26 @@ def test_stream_shapes(n, k, bs, cuda_device):
         assert err < LINEAR_TOL, f"{n}x{k} bs={bs} m={m} {dtype}: {err}"
 
 
+@pytest.mark.parametrize("n,k,bs", [(256, 1024, 64), (200, 2048, 256), (512, 1024, 512), (130, 576, 96), (64, 320, 32),
+                                    (1024, 11008, 128), (48, 256, 128)])
+def test_per_strip_kernel_variants(n, k, bs, cuda_device):
+    # the per-strip kernel's paths: one MMA tile with the single bf16 row staged in shared memory (m = 1), without
+    # staging (m = 2..8, or fp16), two tiles (m = 9..16); whole 256-column chunks with whole-tile blocks (no bounds
+    # predicates) and K / block sizes that need them; more than 16 rows (one launch per 16)
+    for m, dtype in ((1, torch.bfloat16), (1, torch.float16), (2, torch.bfloat16), (7, torch.float16),
+                     (9, torch.bfloat16), (16, torch.float16), (21, torch.bfloat16)):
+        o, x, b, ref = _case(n, k, m, dtype, n + k + m + bs, bias=(m % 2 == 1), bs=bs)
+        y = _run(o, x, b, cuda_device, "gemv")
+        err = rel_max_err(y, ref, report=f"gemv {n}x{k} bs={bs} m={m} {dtype}")
+        assert err < LINEAR_TOL, f"{n}x{k} bs={bs} m={m} {dtype}: {err}"
+        # activations that do not allow 16-byte loads take the same kernels' two-byte path
+        xs = torch.zeros(m, k + 3, dtype=dtype)
+        xs[:, 3:] = x
+        y2 = atlas_wrappers.quantized_linear_forward(xs.to(cuda_device)[:, 3:], _layout(o, cuda_device),
+                                                     None if b is None else b.to(cuda_device), "gemv")
+        assert rel_max_err(y2, ref, report=f"gemv unaligned {n}x{k} m={m}") < LINEAR_TOL
+
+
 @pytest.mark.parametrize("thr", [1.0, 1.5])
 def test_dense_outliers_reach_every_outlier_branch(thr, cuda_device):
     # tens of outliers per 16-row strip and 64-column tile: the streaming kernels' later outlier groups and entry
