@@ -108,9 +108,9 @@ __device__ __forceinline__ void load_x16(const uint16_t *src, uint32_t (&xv)[8])
 // k-tiles of codes in flight per warp.  Two tiles: two CTAs of 8 warps per SM at twice the registers, four k-tiles in
 // flight per warp (the same bytes in flight per SM), the dequantised fragments of a step feeding two MMAs.
 //
-// STAGE (bf16 activations, a single row): the CTA converts the row to fp16 once, into shared memory, instead of every
-// warp converting the fragments of every step in registers -- the kernel is bound by instruction
-// issue (about 120 issue slots per KB of codes, a fifth of them that conversion), not by bytes in flight.
+// STAGE (bf16 activations): every warp converts the columns of its K range to fp16 once, into shared memory (it reads
+// no other columns, so no CTA-wide barrier is needed), instead of converting the fragments of every step in registers
+// for each of its eight row groups -- the kernel is bound by instruction issue, not by bytes in flight.
 //
 // FAST (whole 256-column chunks, blocks of whole 64-column tiles): every batch of a warp is full and a step has one
 // scale block, so the K loop carries no bounds predicates and no per-lane block index.
@@ -161,11 +161,14 @@ __global__ void __launch_bounds__((MT == 1 ? GS_MAX_WARPS : GS_WARPS2) * 32, 2) 
     const int32_t *cptr = p.chunk_ptr + (size_t)strip * (p.k_tiles + 1);
     int e_begin = 0, e_end = 0;
     if (kt0 < kt1) { e_begin = __ldg(cptr + kt0); e_end = __ldg(cptr + kt1); }
+    // an empty slot of an outlier group: row 255 matches no lane; its column is one of this warp's own (with the staged
+    // row a warp reads only what it has written itself)
+    const uint32_t no_entry = 0xff000000u | (uint32_t)(kt0 * 64);
     uint32_t pre_ent[4], pre_val[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         const int e = e_begin + 2 * tig + (q & 1) + (q >> 1) * 8;
-        pre_ent[q] = 0xff000000u;
+        pre_ent[q] = no_entry;
         pre_val[q] = 0;
         if (e < e_end) { pre_ent[q] = __ldg(p.entries + e); pre_val[q] = __ldg(p.ovals + e); }
     }
@@ -180,20 +183,23 @@ __global__ void __launch_bounds__((MT == 1 ? GS_MAX_WARPS : GS_WARPS2) * 32, 2) 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int xs_row_bytes = p.n_cols * 2 + 16;
     if (STAGE) {
-        const int per_row = p.n_cols >> 3;   // 16-byte pieces per row
-        const int total = p.m * per_row;
-        for (int idx = tid; idx < total; idx += blockDim.x) {
-            const int row = p.m == 1 ? 0 : idx / per_row, c = idx - row * per_row;
-            uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.x) + (size_t)row * p.ldx) + c);
-            uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+        // every warp converts the columns of its own K range, the only ones it reads: no CTA-wide barrier
+        const int per_row = (kt1 - kt0) * 8;   // 16-byte pieces per batch row
+        for (int row = 0; row < p.m; ++row) {
+            const uint16_t *src = reinterpret_cast<const uint16_t *>(p.x) + (size_t)row * p.ldx + kt0 * 64;
+            unsigned char *dst = xs_raw + (size_t)row * xs_row_bytes + kt0 * 128;
+            for (int c = lane; c < per_row; c += 32) {
+                uint4 v = __ldg(reinterpret_cast<const uint4 *>(src) + c);
+                uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float lo = __uint_as_float(w4[e] << 16), hi = __uint_as_float(w4[e] & 0xffff0000u);
-                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w4[e]) : "f"(hi), "f"(lo));
+                for (int e = 0; e < 4; ++e) {
+                    const float lo = __uint_as_float(w4[e] << 16), hi = __uint_as_float(w4[e] & 0xffff0000u);
+                    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w4[e]) : "f"(hi), "f"(lo));
+                }
+                *reinterpret_cast<uint4 *>(dst + c * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
-            *reinterpret_cast<uint4 *>(xs_raw + (size_t)row * xs_row_bytes + c * 16) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
         }
-        __syncthreads();
+        __syncwarp();
     }
     // this lane's row of staged activations (rows that do not exist read row 0, as above)
     const unsigned char *xs_lane = xs_raw + (size_t)(g < p.m ? g : 0) * xs_row_bytes;
@@ -287,7 +293,7 @@ __global__ void __launch_bounds__((MT == 1 ? GS_MAX_WARPS : GS_WARPS2) * 32, 2) 
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int e = e0 + 2 * tig + (q & 1) + (q >> 1) * 8;
-            ent[q] = 0xff000000u;
+            ent[q] = no_entry;
             val[q] = 0;
             if (e < e_end) { ent[q] = __ldg(p.entries + e); val[q] = __ldg(p.ovals + e); }
         }
@@ -314,11 +320,11 @@ int launch_gemv_strip(const GemvParams &p, bool vec, cudaStream_t st) {
     const int max_warps = MT == 1 ? GS_MAX_WARPS : GS_WARPS2;
     int nwarps = p.n_chunks < max_warps ? p.n_chunks : max_warps;
     if (nwarps < 4 * MT) nwarps = 4 * MT;  // the reduction needs 128 threads per MMA tile
-    // a single row of bf16 activations is converted once per CTA into shared memory (measured: +3 % at one row, nothing
-    // at two)
+    // one or two rows of bf16 activations are converted once per CTA into shared memory (measured at 1 / 2 / 4 / 8
+    // rows: 3.7 / 3.5 / 3.1 / 2.6 TB/s staged against 3.4 / 3.3 / 3.3 / 3.1 converted per step)
     const size_t stage_bytes = (size_t)p.m * ((size_t)p.n_cols * 2 + 16);
     const bool fast = vec && (p.k_tiles & 3) == 0 && p.bs_shift >= 6;   // whole chunks, blocks of whole tiles
-    const bool stage = MT == 1 && p.dtype == ATLAS_DTYPE_BF16 && vec && p.m == 1 && stage_bytes <= (size_t)GS_STAGE_MAX_BYTES;
+    const bool stage = MT == 1 && p.dtype == ATLAS_DTYPE_BF16 && vec && p.m <= 2 && stage_bytes <= (size_t)GS_STAGE_MAX_BYTES;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((p.n_rows + 15) / 16), 1, 1);
     cfg.blockDim = dim3((unsigned)(nwarps * 32), 1, 1);
