@@ -12,7 +12,8 @@
 // cluster, one __syncthreads.  A warp loads its codes (16-byte loads, 1 KB per warp and step, contiguous in the
 // tile-major layout), scales, first outlier entries and the bias before the dependency wait of programmatic
 // dependent launch, i.e. while the previous kernel of the stream drains; its activations come after the wait,
-// straight from global memory (x is a few KB and stays in L1/L2).  The CTA folds the per-warp partial sums
+// straight from global memory (x is a few KB and stays in L1/L2) -- or, for one or two bf16 rows, through a
+// per-warp fp16 copy in shared memory.  The CTA folds the per-warp partial sums
 // through 8 KB of shared memory in warp order (deterministic, no atomics).
 //
 // Outliers: the side-table is regrouped by 16-row strip and sorted by column (atlas_repack).  A warp turns 16
