@@ -862,7 +862,7 @@ int gemm_splits_for(int64_t m, int64_t n_rows, int64_t n_cols, int sms) {
     const int k_tiles = (int)(n_cols / 64);
     int best = 1;
     int64_t best_cost = 0;
-    for (int s = 1; s <= 8; s *= 2) {
+    for (int s = 1; s <= 16; s *= 2) {
         if (s > 1 && k_tiles / s < 8) break;
         const int64_t cost = ceil_div_i64(tiles * s, sms) * (ceil_div_i64(k_tiles, s) + 12);
         if (s == 1 || cost < best_cost) { best = s; best_cost = cost; }
@@ -905,7 +905,10 @@ extern "C" size_t atlas_qlinear_gemm_workspace_bytes(int64_t m, int64_t n_rows, 
     // fp16 copy of x (bf16 or strided input), then room for up to 8 fp32 K-slice partial outputs
     // (only decode-sized batches are ever sliced)
     const size_t xcopy = ((size_t)m * (size_t)n_cols * 2 + 255) & ~(size_t)255;
-    const size_t part = atlas::gemm_bn_for(m) <= 64 ? (size_t)8 * (size_t)m * (size_t)n_rows * 4 : 0;
+    // (one fp32 slice of the output per K slice; one even without slicing, for the gathered form)
+    const size_t part = atlas::gemm_bn_for(m) <= 64
+                            ? (size_t)atlas::gemm_splits_for(m, n_rows, n_cols, atlas::gemm_sm_count()) * (size_t)m * (size_t)n_rows * 4
+                            : 0;
     return atlas::GM_WS_HEADER + xcopy + part;
 }
 
